@@ -354,15 +354,18 @@ int spd_residual_rmsnorm(void* out, float* x, const void* a, const void* b, cons
 /* x[r, :] = table[idx[r], :] as fp32 (embedding lookup into the fp32 residual stream) */
 int spd_embed_f32(float* x, const void* table, const int64_t* idx, int64_t rows, int64_t dim,
                   int64_t table_rows, int dtype, spd_stream_t stream);
-/* out[r, i] = act(x[r, i]) * x[r, inter + i]; act 0 = SiLU, 1 = tanh-form GELU.  x [rows, 2 inter] */
-int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int act, int dtype,
+/* out[r, i] = act(x[r, i]) * x[r, inter + i]; act 0 = SiLU, 1 = tanh-form GELU.  x [rows, 2 inter].
+ * act 2: with g = min(x[r, i], p0) and u = clamp(x[r, inter + i], -p0, p0), out = g sigmoid(p1 g) (u + 1)
+ * (p0, p1 are read by act 2 only) */
+int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int act, float p0, float p1, int dtype,
                     spd_stream_t stream);
-/* out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(g[t, h, :]);  o fp32 [tokens, heads *
- * vdim] contiguous, g dtype with row stride g_stride, out dtype contiguous */
+/* out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * gate(g[t, h, :]), gate = SiLU (gate_act 0) or
+ * sigmoid (gate_act 1);  o fp32 [tokens, heads * vdim] contiguous, g dtype with row stride g_stride, out dtype
+ * contiguous */
 /* w (nullable, dtype): a weight on the normed values, element h * w_head_stride + c for head h (stride 0:
  * one vector of vdim shared by the heads) */
 int spd_headnorm_gate(void* out, const float* o, const void* g, int64_t tokens, int heads, int vdim,
-                      int64_t g_stride, float eps, const void* w, int w_head_stride, int dtype,
+                      int64_t g_stride, float eps, const void* w, int w_head_stride, int gate_act, int dtype,
                       spd_stream_t stream);
 /* C = A W^T on the CUDA cores with fp32 accumulation in ascending-k order (any M, N, K; any dtype).
  * tile_group != NULL: rows of A are grouped in 128-row tiles (spd_moe_align) and rows
@@ -416,13 +419,13 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
  * fp32 is read at slot req_pool_indices[r] unless the request starts at position 0 (zero state then),
  * and written back.  Decode (seq_lens != NULL) or ragged extend as spd_attn_general; in decode rows
  * whose out_cache_loc is 0 (padding of a captured batch) leave the state untouched.  o fp32 [tokens,
- * heads * v_dim]. */
+ * heads * v_dim].  in_act 1: q, k and v pass through SiLU (in fp32) as they are read, before the rotation. */
 int spd_retention(float* o, const void* q, const void* k, const void* v, float* state,
                   const int64_t* req_pool_indices, const int64_t* seq_lens, const int64_t* out_cache_loc,
                   const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
                   int64_t batch, int num_heads, int head_dim, int v_dim, int64_t q_stride, int64_t k_stride,
                   int64_t v_stride, const float* decay, const float* cos_sin, int rot_dims,
-                  int64_t max_positions, float k_scale, int dtype, spd_stream_t stream);
+                  int64_t max_positions, float k_scale, int in_act, int dtype, spd_stream_t stream);
 
 /* spd_residual_rmsnorm with a second weight: out2 = the same normed row times (weight_offset + w2)
  * (out2 and w2 both NULL or both given) */
@@ -477,6 +480,53 @@ int spd_head_gate_sigmoid(void* out, const void* o, const void* g, int64_t token
                           int64_t o_stride, int64_t g_stride, int dtype, spd_stream_t stream);
 /* x[i] *= alpha for i < n */
 int spd_scale_f32(float* x, int64_t n, float alpha, spd_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * A residual kept as several streams (hyper-connections), the rotary step of an attention with
+ * biased projections, and the exponentially gated matrix memory (csrc/stream_ops.cu, matrix_memory.cu)
+ * ------------------------------------------------------------------------------------------- */
+/* X[r, s, :] = table[idx[r], :] / sqrt(mean(.^2) + eps) * w for s < streams (X fp32 [rows, streams, dim];
+ * w NULL: the raw row) */
+int spd_embed_norm_streams(float* X, const void* table, const int64_t* idx, const void* w, int64_t rows,
+                           int64_t dim, int64_t table_rows, int streams, float eps, int dtype,
+                           spd_stream_t stream);
+/* Per token r (X fp32 [tokens, streams, dim], in place):
+ *   write (a != NULL): y = sa a[r] + sb b[r] + sbias bias (b, bias nullable; a, b dtype [tokens, dim], bias fp32
+ *     [dim]); X'[t] = sum_s mix[s * streams + t] X[s] + mult * outw[t] * y  (mix, outw fp32)
+ *   read (out != NULL): u = sum_s inw[s] X'[s] (inw NULL: all 1); out[r] = u / sqrt(mean(u^2) + eps) * w
+ * rows_idx != NULL (read only): out row r comes from token rows_idx[r]; `rows` counts out rows. */
+int spd_streams_mix_norm(void* out, float* X, const void* a, const void* b, const float* bias, float sa, float sb,
+                         float sbias, const float* mix, const float* outw, float mult, const float* inw,
+                         const void* w, const int64_t* rows_idx, int64_t rows, int64_t dim, int streams,
+                         float eps, int dtype, spd_stream_t stream);
+/* q_out[t] = rot(q[t] + q_bias), k_pool[loc[t]] = rot(k[t] + k_bias), rotation of the first rot_dims dimensions
+ * of every head by position positions[t] (rotate-half pairing, cos_sin [max_positions, rot_dims] fp32 =
+ * cos || sin); v_pool[loc[t]] = v[t], or, with v NULL, the biased keys before the rotation (v_pool nullable;
+ * biases fp32, nullable). */
+int spd_rotary_bias_store(void* q_out, const void* q, const void* k, const void* v, const float* q_bias,
+                          const float* k_bias, void* k_pool, void* v_pool, const int64_t* loc,
+                          const int64_t* positions, const float* cos_sin, int rot_dims, int64_t max_positions,
+                          int64_t tokens, int num_q_heads, int num_kv_heads, int head_dim, int v_dim,
+                          int64_t q_stride, int64_t k_stride, int64_t v_stride, int64_t q_out_stride, int dtype,
+                          spd_stream_t stream);
+/* floats per slot of the vector state of spd_matrix_memory: per head and block of 32 value columns, n
+ * [head_dim] and m */
+int64_t spd_matrix_memory_vector_dim(int num_heads, int head_dim, int v_dim);
+/* Exponentially gated matrix memory per (request, head): with i = softcap(zi + i_bias), f =
+ * logsigmoid(softcap(zf + f_bias)), softcap(z) = cap tanh(z / cap) (cap <= 0: z),
+ *   m' = max(f + m, i); S' = e^(f + m - m') S + e^(i - m') k v^T; n' = e^(f + m - m') n + e^(i - m') k;
+ *   o = S'^T (q q_scale) / (max(|n' . q q_scale|, e^(-m')) + 1e-6)
+ * S [slots, heads, head_dim, v_dim] and vec [slots, vec_stride] fp32 at slot req_pool_indices[r] (S = n = 0,
+ * m = 0 for a request that starts at position 0), written back.  q, k [tokens, heads * head_dim], v [tokens,
+ * heads * v_dim], zi, zf [tokens, heads] (dtype, row strides given); biases fp32 [heads], nullable.  Decode /
+ * ragged extend and padded rows as spd_retention.  o fp32 [tokens, heads * v_dim]. */
+int spd_matrix_memory(float* o, const void* q, const void* k, const void* v, const void* zi, const void* zf,
+                      float* state, float* vec, int64_t vec_stride, const int64_t* req_pool_indices,
+                      const int64_t* seq_lens, const int64_t* out_cache_loc, const int32_t* prefix_lens,
+                      const int32_t* extend_lens, const int32_t* extend_start_loc, int64_t batch, int num_heads,
+                      int head_dim, int v_dim, int64_t q_stride, int64_t k_stride, int64_t v_stride,
+                      int64_t zi_stride, int64_t zf_stride, const float* i_bias, const float* f_bias, float cap,
+                      float q_scale, int dtype, spd_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -91,8 +91,8 @@ SIGNATURES = {
                           _i64, _i, _p]),
     "spd_residual_rmsnorm": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _f, _f, _i, _p]),
     "spd_embed_f32": (_i, [_p, _p, _p, _i64, _i64, _i64, _i, _p]),
-    "spd_act_and_mul": (_i, [_p, _p, _i64, _i64, _i, _i, _p]),
-    "spd_headnorm_gate": (_i, [_p, _p, _p, _i64, _i, _i, _i64, _f, _p, _i, _i, _p]),
+    "spd_act_and_mul": (_i, [_p, _p, _i64, _i64, _i, _f, _f, _i, _p]),
+    "spd_headnorm_gate": (_i, [_p, _p, _p, _i64, _i, _i, _i64, _f, _p, _i, _i, _i, _p]),
     "spd_linear_simt": (_i, [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _i64, _i, _i, _p]),
     "spd_moe_route_scores": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _i, _i, _f, _p, _i, _i, _p]),
     "spd_residual_rmsnorm2": (_i, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, _f, _i, _p]),
@@ -120,7 +120,19 @@ SIGNATURES = {
     "spd_retention": (
         _i,
         [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i64, _i64, _p, _p, _i, _i64, _f,
-         _i, _p],
+         _i, _i, _p],
+    ),
+    "spd_embed_norm_streams": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _i, _f, _i, _p]),
+    "spd_streams_mix_norm": (_i, [_p, _p, _p, _p, _p, _f, _f, _f, _p, _p, _f, _p, _p, _p, _i64, _i64, _i, _f, _i, _p]),
+    "spd_rotary_bias_store": (
+        _i,
+        [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i64, _i64, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i, _p],
+    ),
+    "spd_matrix_memory_vector_dim": (_i64, [_i, _i, _i]),
+    "spd_matrix_memory": (
+        _i,
+        [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
+         _p, _p, _f, _f, _i, _p],
     ),
     "spd_attn_prefill_simt": (
         _i,

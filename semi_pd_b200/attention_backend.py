@@ -181,10 +181,12 @@ class SpdAttnBackend(AttentionBackend):
     def forward_retention(self, q, k, v, layer, forward_batch: ForwardBatch):
         """Retention mixer (decayed linear attention) over the request's recurrent state slot;
         `layer` carries num_heads, head_dim, v_head_dim, decay (fp32 [heads]), cos_sin_cache, rotary_dim,
-        k_scale and layer_id.  → o fp32 [T, heads · v_head_dim]; the state is updated in place."""
+        k_scale and layer_id, optionally in_act ("silu": q, k, v are activated as the kernel reads them).
+        → o fp32 [T, heads · v_head_dim]; the state is updated in place."""
         state = forward_batch.token_to_kv_pool.state_pool.get_state(layer.layer_id)
         common = dict(num_heads=layer.num_heads, head_dim=layer.head_dim, v_dim=layer.v_head_dim, decay=layer.decay,
-                      cos_sin=layer.cos_sin_cache, rot_dims=layer.rotary_dim, k_scale=layer.k_scale)
+                      cos_sin=layer.cos_sin_cache, rot_dims=layer.rotary_dim, k_scale=layer.k_scale,
+                      in_act=getattr(layer, "in_act", None))
         if forward_batch.forward_mode.is_decode():
             return ops.retention(q, k, v, state, forward_batch.req_pool_indices, seq_lens=forward_batch.seq_lens,
                                  out_cache_loc=forward_batch.out_cache_loc, **common)
@@ -208,6 +210,27 @@ class SpdAttnBackend(AttentionBackend):
                                     head_dim=layer.head_dim, v_dim=layer.v_head_dim, form=layer.form,
                                     q_scale=layer.q_scale, tau=layer.tau, z_bias=layer.z_bias, bonus=layer.bonus,
                                     **self._batch_rows(forward_batch))
+
+    def forward_matrix_memory(self, q, k, v, zi, zf, layer, forward_batch: ForwardBatch):
+        """Exponentially gated matrix memory over the request's state slot (matrix state + the layer's vector
+        state, which holds the normaliser and the running maximum).  `layer` carries num_heads, head_dim,
+        v_head_dim, layer_id, i_bias / f_bias (fp32 [heads] or None), gate_cap and q_scale; zi / zf [T, heads] are
+        the raw gate projections.  → o fp32 [T, heads · v_head_dim]."""
+        pool = forward_batch.token_to_kv_pool.state_pool
+        return ops.matrix_memory(q, k, v, zi, zf, pool.get_state(layer.layer_id), pool.get_shift(layer.layer_id),
+                                 forward_batch.req_pool_indices, num_heads=layer.num_heads, head_dim=layer.head_dim,
+                                 v_dim=layer.v_head_dim, i_bias=layer.i_bias, f_bias=layer.f_bias, cap=layer.gate_cap,
+                                 q_scale=layer.q_scale, **self._batch_rows(forward_batch))
+
+    def forward_rotary_store(self, q, k, v, layer: RadixAttention, forward_batch: ForwardBatch, q_bias=None,
+                             k_bias=None, cos_sin=None, rot_dims: int = 0):
+        """Bias + partial rotation of q and k by the batch's positions, with the KV write fused: rotated keys into
+        the layer's key pool, `v` (or, v None, the biased keys before the rotation) into its value pool.
+        → rotated q; the attention call that follows passes save_kv_cache=False."""
+        k_buf, v_buf = forward_batch.token_to_kv_pool.get_kv_buffer(layer.layer_id)
+        return ops.rotary_bias_store(q, k, v, q_bias, k_bias, k_buf, v_buf, forward_batch.out_cache_loc,
+                                     forward_batch.positions, cos_sin, rot_dims, layer.tp_q_head_num,
+                                     layer.tp_k_head_num, layer.qk_head_dim, layer.v_head_dim)
 
     def forward_token_shift(self, h, mu, layer, forward_batch: ForwardBatch):
         """Token shift of a mixer's input: → [n_mix, T, dim] = h + (previous row − h) · mu[s]; the row before a

@@ -67,6 +67,11 @@ class ModelConfig:
     # model_type "nupovik": layer_specs has one entry per layer RUN (a looped block repeats its layers, each
     # run with a cache / state of its own); logits are multiplied by logit_scale
     logit_scale: float = 1.0
+    # model_type "matepel": the residual is kept as `num_streams` parallel copies that every sublayer reads through
+    # a weighted sum and writes back through a mixing matrix (None: one plain residual); a sublayer's output is
+    # multiplied by residual_mult before it is added
+    num_streams: Optional[int] = None
+    residual_mult: float = 1.0
 
     @property
     def context_len(self) -> int:
@@ -180,8 +185,51 @@ def _nupovik_config(path: str, cfg: dict, **overrides) -> ModelConfig:
     return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "nupovik", **kw)
 
 
+def _matepel_config(path: str, cfg: dict, **overrides) -> ModelConfig:
+    """config.json of the Matepel family: {"architecture", "vocab", "width", "norm": {"eps"}, "residual_mult",
+    "streams", "layers": [{"type": "lightning" | "parallel", "mixer": {...}, "mlp": {"kind": "dense", "ff",
+    "limit"} | null}, ...]}.  A "lightning" mixer is {heads, dim, vdim, decay: [heads]}; a "parallel" mixer is
+    {"left": {heads, kv_heads, dim, vdim, scale, rot: {dims, base, scaling: {factor, original, fast, slow}}},
+    "right": {heads, dim, vdim, gate_cap}, "left_scale", "right_scale"}.  Every size and constant is carried per
+    layer in `layer_specs`."""
+    layers = [dict(spec) for spec in cfg["layers"]]
+    for i, spec in enumerate(layers):
+        if spec["type"] not in ("lightning", "parallel"):
+            raise ValueError(f"layer {i}: unknown mixer type {spec['type']!r}")
+        if spec.get("mlp") is not None and spec["mlp"].get("kind") != "dense":
+            raise ValueError(f"layer {i}: unknown feed-forward kind {spec['mlp'].get('kind')!r}")
+        m = spec["mixer"]
+        if spec["type"] == "lightning":
+            if len(m["decay"]) != int(m["heads"]):
+                raise ValueError(f"layer {i}: {len(m['decay'])} decays for {m['heads']} heads")
+        else:
+            left = m["left"]
+            if int(left["heads"]) % int(left.get("kv_heads", left["heads"])):
+                raise ValueError(f"layer {i}: {left['heads']} heads are not a multiple of {left['kv_heads']} kv heads")
+            if int(left.get("vdim", left["dim"])) != int(left["dim"]):
+                raise ValueError(f"layer {i}: the values are the keys, so vdim {left['vdim']} must equal dim {left['dim']}")
+            rot = left.get("rot") or {}
+            if int(rot.get("dims") or 0) % 2 or int(rot.get("dims") or 0) > int(left["dim"]):
+                raise ValueError(f"layer {i}: rot.dims {rot.get('dims')} must be even and at most dim {left['dim']}")
+    streams = cfg.get("streams")
+    if streams is not None and not 1 <= int(streams) <= 8:
+        raise ValueError(f"streams {streams}: 1 to 8 are supported")
+    lefts = [s["mixer"]["left"] for s in layers if s["type"] == "parallel"]
+    kw = dict(model_type="matepel", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+              num_hidden_layers=len(layers), rms_norm_eps=float(cfg["norm"]["eps"]), layer_specs=layers,
+              num_streams=int(streams) if streams is not None else None,
+              residual_mult=float(cfg.get("residual_mult", 1.0)),
+              # summary fields other components print or size by; the per-layer values rule
+              num_attention_heads=max([int(m["heads"]) for m in lefts] or [1]),
+              num_key_value_heads=max([int(m.get("kv_heads", m["heads"])) for m in lefts] or [1]),
+              head_dim=max([int(m["dim"]) for m in lefts] or [1]), intermediate_size=0,
+              max_position_embeddings=int(cfg.get("context", 8192)))
+    kw.update(overrides)
+    return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "matepel", **kw)
+
+
 # config.json "architecture" -> reader
-_ARCHITECTURE_READERS = {"Rimidra": _rimidra_config, "Nupovik": _nupovik_config}
+_ARCHITECTURE_READERS = {"Rimidra": _rimidra_config, "Nupovik": _nupovik_config, "Matepel": _matepel_config}
 
 
 def load_model_config(path: str, **overrides) -> ModelConfig:

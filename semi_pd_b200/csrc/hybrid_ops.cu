@@ -28,6 +28,15 @@ __device__ __forceinline__ float gelu_tanh_precise(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 __device__ __forceinline__ float sigmoid_precise(float z) { return 1.0f / (1.0f + expf(-z)); }
+// act(g) * u of a gated feed-forward.  act 0 SiLU, 1 tanh-form GELU, 2 clamped sigmoid-linear unit:
+// g' = min(g, p0), u' = clamp(u, -p0, p0), g' sigmoid(p1 g') (u' + 1)
+__device__ __forceinline__ float gated_act(float g, float u, int act, float p0, float p1) {
+  if (act == 0) return silu_precise(g) * u;
+  if (act == 1) return gelu_tanh_precise(g) * u;
+  g = fminf(g, p0);
+  u = fminf(fmaxf(u, -p0), p0);
+  return g * sigmoid_precise(p1 * g) * (u + 1.0f);
+}
 
 // one CTA per row: x += a (+ b); out = x * rsqrt(mean(x^2) + eps) * (off + w); a second weight w2
 // gives a second normed copy out2 of the same row (layers whose two sublayers have a norm each)
@@ -77,7 +86,8 @@ embed_f32_kernel(float* __restrict__ x, const T* __restrict__ table, const int64
 // vector form: inter a multiple of the vector width, 16-byte aligned pointers
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
-act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t inter, int act) {
+act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t inter, int act, float p0,
+                       float p1) {
   griddep_wait();
   griddep_launch_dependents();
   constexpr int N = Vec16<T>::kN;
@@ -88,8 +98,7 @@ act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t row
     Vec16<T> o;
 #pragma unroll
     for (int k = 0; k < N; ++k) {
-      const float gv = to_f32<T>(g.e()[k]);
-      o.e()[k] = from_f32<T>((act == 0 ? silu_precise(gv) : gelu_tanh_precise(gv)) * to_f32<T>(u.e()[k]));
+      o.e()[k] = from_f32<T>(gated_act(to_f32<T>(g.e()[k]), to_f32<T>(u.e()[k]), act, p0, p1));
     }
     stv(out + r * inter + c, o);
   }
@@ -97,7 +106,8 @@ act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t row
 
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
-act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t inter, int act) {
+act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int64_t inter, int act, float p0,
+                   float p1) {
   griddep_wait();
   griddep_launch_dependents();
   const int64_t n = rows * inter;
@@ -105,8 +115,7 @@ act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, i
     const int64_t r = i / inter, c = i - r * inter;
     const float g = to_f32<T>(x[r * 2 * inter + c]);
     const float u = to_f32<T>(x[r * 2 * inter + inter + c]);
-    const float a = act == 0 ? silu_precise(g) : gelu_tanh_precise(g);
-    out[i] = from_f32<T>(a * u);
+    out[i] = from_f32<T>(gated_act(g, u, act, p0, p1));
   }
 }
 
@@ -114,7 +123,8 @@ act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, i
 template <typename T>
 __global__ void __launch_bounds__(128)
 headnorm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ g, int64_t tokens,
-                     int heads, int vdim, int64_t g_stride, float eps, const T* __restrict__ w, int w_head_stride) {
+                     int heads, int vdim, int64_t g_stride, float eps, const T* __restrict__ w, int w_head_stride,
+                     int gate_act) {
   griddep_wait();
   griddep_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -128,7 +138,8 @@ headnorm_gate_kernel(T* __restrict__ out, const float* __restrict__ o, const T* 
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)vdim + eps);
   for (int c = lane; c < vdim; c += 32) {
-    const float gate = silu_precise(to_f32<T>(g[t * g_stride + (int64_t)h * vdim + c]));
+    const float gz = to_f32<T>(g[t * g_stride + (int64_t)h * vdim + c]);
+    const float gate = gate_act == 0 ? silu_precise(gz) : sigmoid_precise(gz);
     const float wt = w != nullptr ? to_f32<T>(w[h * w_head_stride + c]) : 1.f;
     out[(t * heads + h) * (int64_t)vdim + c] = from_f32<T>(orow[c] * inv * wt * gate);
   }
@@ -468,10 +479,10 @@ int spd_embed_f32(float* x, const void* table, const int64_t* idx, int64_t rows,
   return 0;
 }
 
-int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int act, int dtype,
+int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int act, float p0, float p1, int dtype,
                     spd_stream_t stream) {
   SPD_REQUIRE(out && x, SPD_E_BADARG, "spd_act_and_mul: null pointer");
-  SPD_REQUIRE(rows >= 0 && inter > 0 && (act == 0 || act == 1), SPD_E_BADARG, "spd_act_and_mul: bad arguments");
+  SPD_REQUIRE(rows >= 0 && inter > 0 && act >= 0 && act <= 2, SPD_E_BADARG, "spd_act_and_mul: bad arguments");
   if (rows == 0) return 0;
   SPD_DISPATCH_ANY(dtype, {
     constexpr int N = 16 / (int)sizeof(T);
@@ -481,26 +492,27 @@ int spd_act_and_mul(void* out, const void* x, int64_t rows, int64_t inter, int a
     const unsigned grid = (unsigned)(blocks < 8192 ? blocks : 8192);
     if (vec) {
       SPD_CUDA(launch(act_and_mul_vec_kernel<T>, dim3(grid), dim3(kRowThreads), 0, as_stream(stream), pdl_enabled(),
-                      (T*)out, (const T*)x, rows, inter, act));
+                      (T*)out, (const T*)x, rows, inter, act, p0, p1));
     } else {
       SPD_CUDA(launch(act_and_mul_kernel<T>, dim3(grid), dim3(kRowThreads), 0, as_stream(stream), pdl_enabled(),
-                      (T*)out, (const T*)x, rows, inter, act));
+                      (T*)out, (const T*)x, rows, inter, act, p0, p1));
     }
   });
   return 0;
 }
 
 int spd_headnorm_gate(void* out, const float* o, const void* g, int64_t tokens, int heads, int vdim,
-                      int64_t g_stride, float eps, const void* w, int w_head_stride, int dtype,
+                      int64_t g_stride, float eps, const void* w, int w_head_stride, int gate_act, int dtype,
                       spd_stream_t stream) {
   SPD_REQUIRE(out && o && g, SPD_E_BADARG, "spd_headnorm_gate: null pointer");
+  SPD_REQUIRE(gate_act == 0 || gate_act == 1, SPD_E_BADARG, "spd_headnorm_gate: gate_act is 0 (SiLU) or 1 (sigmoid)");
   SPD_REQUIRE(tokens >= 0 && heads > 0 && vdim > 0, SPD_E_BADARG, "spd_headnorm_gate: bad sizes");
   if (tokens == 0) return 0;
   const int64_t items = tokens * heads;
   SPD_DISPATCH_ANY(dtype, {
     SPD_CUDA(launch(headnorm_gate_kernel<T>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, as_stream(stream),
                     pdl_enabled(), (T*)out, o, (const T*)g, tokens, heads, vdim, g_stride, eps, (const T*)w,
-                    w_head_stride));
+                    w_head_stride, gate_act));
   });
   return 0;
 }

@@ -26,6 +26,9 @@
 
 namespace spd {
 
+// activation applied to q, k and v as they are read (before rotation): 0 none, 1 SiLU
+__device__ __forceinline__ float ret_in_act(float x, int act) { return act == 1 ? x / (1.0f + expf(-x)) : x; }
+
 constexpr int kRetTok = 16;   // tokens staged per block (extend); decode stages its one token
 constexpr int kRetCols = 32;  // value columns per CTA
 
@@ -37,7 +40,7 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
                  const int32_t* __restrict__ prefix_lens, const int32_t* __restrict__ extend_lens,
                  const int32_t* __restrict__ extend_start_loc, int H, int dk, int dv, int64_t q_stride,
                  int64_t k_stride, int64_t v_stride, const float* __restrict__ decay,
-                 const float* __restrict__ cos_sin, int rot, int64_t max_positions, float k_scale) {
+                 const float* __restrict__ cos_sin, int rot, int64_t max_positions, float k_scale, int in_act) {
   static_assert(ROWS % 4 == 0, "rows per thread are read as float4");
   constexpr int DKP = W * ROWS;  // padded head_dim
   constexpr int NT = W * 32;
@@ -119,36 +122,36 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
         if (ASYNC) {
           const T* qr = rq + tt * dk;
           const T* kr = rk + tt * dk;
-          qv = to_f32<T>(qr[d]);
-          kv = to_f32<T>(kr[d]);
+          qv = ret_in_act(to_f32<T>(qr[d]), in_act);
+          kv = ret_in_act(to_f32<T>(kr[d]), in_act);
           if (d < rot) {
             const int i = d < half ? d : d - half;
             const float cv = cs[tt * rot + i], sn = cs[tt * rot + half + i];
             if (d < half) {
-              qv = qv * cv - to_f32<T>(qr[d + half]) * sn;
-              kv = kv * cv - to_f32<T>(kr[d + half]) * sn;
+              qv = qv * cv - ret_in_act(to_f32<T>(qr[d + half]), in_act) * sn;
+              kv = kv * cv - ret_in_act(to_f32<T>(kr[d + half]), in_act) * sn;
             } else {
-              qv = qv * cv + to_f32<T>(qr[d - half]) * sn;
-              kv = kv * cv + to_f32<T>(kr[d - half]) * sn;
+              qv = qv * cv + ret_in_act(to_f32<T>(qr[d - half]), in_act) * sn;
+              kv = kv * cv + ret_in_act(to_f32<T>(kr[d - half]), in_act) * sn;
             }
           }
         } else {
           const int64_t row = row0 + t0 + tt;
           const T* qr = q + row * q_stride + (int64_t)h * dk;
           const T* kr = k + row * k_stride + (int64_t)h * dk;
-          qv = to_f32<T>(qr[d]);
-          kv = to_f32<T>(kr[d]);
+          qv = ret_in_act(to_f32<T>(qr[d]), in_act);
+          kv = ret_in_act(to_f32<T>(kr[d]), in_act);
           if (d < rot) {
             int64_t p = pos0 + t0 + tt;
             p = p < max_positions ? p : max_positions - 1;
             const int i = d < half ? d : d - half;
             const float cv = cos_sin[p * rot + i], sn = cos_sin[p * rot + half + i];
             if (d < half) {
-              qv = qv * cv - to_f32<T>(qr[d + half]) * sn;
-              kv = kv * cv - to_f32<T>(kr[d + half]) * sn;
+              qv = qv * cv - ret_in_act(to_f32<T>(qr[d + half]), in_act) * sn;
+              kv = kv * cv - ret_in_act(to_f32<T>(kr[d + half]), in_act) * sn;
             } else {
-              qv = qv * cv + to_f32<T>(qr[d - half]) * sn;
-              kv = kv * cv + to_f32<T>(kr[d - half]) * sn;
+              qv = qv * cv + ret_in_act(to_f32<T>(qr[d - half]), in_act) * sn;
+              kv = kv * cv + ret_in_act(to_f32<T>(kr[d - half]), in_act) * sn;
             }
           }
         }
@@ -158,10 +161,10 @@ retention_kernel(float* __restrict__ o, const T* __restrict__ q, const T* __rest
     }
     for (int idx = threadIdx.x; idx < nt * kRetCols; idx += NT) {
       if (ASYNC) {
-        vs[idx] = to_f32<T>(rv[idx]);
+        vs[idx] = ret_in_act(to_f32<T>(rv[idx]), in_act);
       } else {
         const int tt = idx / kRetCols, cl = idx - tt * kRetCols;
-        vs[idx] = col0 + cl < dv ? to_f32<T>(v[(row0 + t0 + tt) * v_stride + (int64_t)h * dv + col0 + cl]) : 0.f;
+        vs[idx] = col0 + cl < dv ? ret_in_act(to_f32<T>(v[(row0 + t0 + tt) * v_stride + (int64_t)h * dv + col0 + cl]), in_act) : 0.f;
       }
     }
     __syncthreads();  // staging complete (ASYNC: the raw area is free again)
@@ -210,7 +213,7 @@ int retention_launch(dim3 grid, size_t smem, cudaStream_t stream, float* o, cons
                      const int64_t* out_cache_loc, const int32_t* prefix_lens, const int32_t* extend_lens,
                      const int32_t* extend_start_loc, int H, int dk, int dv, int64_t q_stride, int64_t k_stride,
                      int64_t v_stride, const float* decay, const float* cos_sin, int rot, int64_t max_positions,
-                     float k_scale) {
+                     float k_scale, int in_act) {
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     SPD_CUDA(cudaFuncSetAttribute(retention_kernel<T, W, ROWS, ASYNC, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -220,7 +223,7 @@ int retention_launch(dim3 grid, size_t smem, cudaStream_t stream, float* o, cons
   SPD_CUDA(launch(retention_kernel<T, W, ROWS, ASYNC, TOK>, grid, dim3(W * 32), smem, stream, /*pdl=*/false, o, (const T*)q,
                   (const T*)k, (const T*)v, state, req_pool_indices, seq_lens, out_cache_loc, prefix_lens, extend_lens,
                   extend_start_loc, H, dk, dv, q_stride, k_stride, v_stride, decay, cos_sin, rot, max_positions,
-                  k_scale));
+                  k_scale, in_act));
   return 0;
 }
 
@@ -235,7 +238,7 @@ int spd_retention(float* o, const void* q, const void* k, const void* v, float* 
                   const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
                   int64_t batch, int num_heads, int head_dim, int v_dim, int64_t q_stride, int64_t k_stride,
                   int64_t v_stride, const float* decay, const float* cos_sin, int rot_dims,
-                  int64_t max_positions, float k_scale, int dtype, spd_stream_t stream) {
+                  int64_t max_positions, float k_scale, int in_act, int dtype, spd_stream_t stream) {
   SPD_REQUIRE(o && q && k && v && state && req_pool_indices && decay, SPD_E_BADARG, "spd_retention: null pointer");
   SPD_REQUIRE(seq_lens != nullptr || (prefix_lens && extend_lens && extend_start_loc), SPD_E_BADARG,
               "spd_retention: extend needs prefix_lens, extend_lens and extend_start_loc");
@@ -243,6 +246,7 @@ int spd_retention(float* o, const void* q, const void* k, const void* v, float* 
               "spd_retention: head_dim %d above 256", head_dim);
   SPD_REQUIRE(rot_dims >= 0 && rot_dims <= head_dim && rot_dims % 2 == 0 && (rot_dims == 0 || (cos_sin && max_positions > 0)),
               SPD_E_BADARG, "spd_retention: bad rotation (rot_dims %d)", rot_dims);
+  SPD_REQUIRE(in_act == 0 || in_act == 1, SPD_E_BADARG, "spd_retention: in_act is 0 (none) or 1 (SiLU)");
   if (batch == 0) return 0;
   const dim3 grid((unsigned)batch, (unsigned)num_heads, (unsigned)((v_dim + kRetCols - 1) / kRetCols));
   // warps x rows per thread covering head_dim: 8 rows per thread up to 128, 16 above
@@ -262,7 +266,7 @@ int spd_retention(float* o, const void* q, const void* k, const void* v, float* 
 #define SPD_RET_ARGS                                                                                              \
   as_stream(stream), o, q, k, v, state, req_pool_indices, seq_lens, out_cache_loc, prefix_lens, extend_lens,      \
       extend_start_loc, num_heads, head_dim, v_dim, q_stride, k_stride, v_stride, decay, cos_sin, rot_dims,       \
-      max_positions, k_scale
+      max_positions, k_scale, in_act
 #define SPD_RET_SHAPE(W, ROWS)                                                                                    \
   return decode     ? retention_launch<T, W, ROWS, false, 1>(grid, smem, SPD_RET_ARGS)                            \
          : async_ok ? retention_launch<T, W, ROWS, true, kRetTok>(grid, smem_async, SPD_RET_ARGS)                 \

@@ -565,22 +565,24 @@ def residual_rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float
     return out
 
 
-def act_and_mul(x: torch.Tensor, act: str = "silu") -> torch.Tensor:
-    """act(x[:, :I]) · x[:, I:], act in {"silu", "gelu_tanh"}; any of the three dtypes."""
+def act_and_mul(x: torch.Tensor, act: str = "silu", limit: float = 0.0, slope: float = 1.0) -> torch.Tensor:
+    """act(x[:, :I]) · x[:, I:], act in {"silu", "gelu_tanh"}; any of the three dtypes.  act "clamped_swish":
+    with g = min(x[:, :I], limit) and u = clamp(x[:, I:], ±limit), g · sigmoid(slope · g) · (u + 1)."""
     _cuda(x)
     if x.dim() != 2 or not x.is_contiguous():
         raise RuntimeError("act_and_mul: x must be contiguous [rows, 2 I]")
     inter = x.shape[1] // 2
     out = torch.empty((x.shape[0], inter), device=x.device, dtype=x.dtype)
-    check(lib.spd_act_and_mul(out.data_ptr(), x.data_ptr(), x.shape[0], inter, {"silu": 0, "gelu_tanh": 1}[act],
+    check(lib.spd_act_and_mul(out.data_ptr(), x.data_ptr(), x.shape[0], inter,
+                              {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}[act], float(limit), float(slope),
                               _dta(x), _stream()), "spd_act_and_mul")
     return out
 
 
 def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, eps: float,
-                  weight: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """o fp32 [T, heads·vdim] → per-head o / rms(o) [· weight] · silu(gate), in gate's dtype.  weight: [vdim]
-    (shared by the heads) or [heads·vdim], in gate's dtype."""
+                  weight: Optional[torch.Tensor] = None, gate_act: str = "silu") -> torch.Tensor:
+    """o fp32 [T, heads·vdim] → per-head o / rms(o) [· weight] · act(gate), act SiLU or sigmoid, in gate's dtype.
+    weight: [vdim] (shared by the heads) or [heads·vdim], in gate's dtype.  heads = 1 norms the whole row."""
     _cuda(o, gate, weight)
     w_stride = 0
     if weight is not None:
@@ -592,7 +594,8 @@ def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, ep
     T = o.shape[0]
     out = torch.empty((T, heads * vdim), device=o.device, dtype=gate.dtype)
     check(lib.spd_headnorm_gate(out.data_ptr(), o.data_ptr(), gate.data_ptr(), T, heads, vdim, gate.stride(0),
-                                float(eps), _ptr(weight), w_stride, _dta(gate), _stream()), "spd_headnorm_gate")
+                                float(eps), _ptr(weight), w_stride, {"silu": 0, "sigmoid": 1}[gate_act], _dta(gate),
+                                _stream()), "spd_headnorm_gate")
     return out
 
 
@@ -927,9 +930,10 @@ def attn_general(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, re
 def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, req_pool_indices,
               num_heads: int, head_dim: int, v_dim: int, decay: torch.Tensor, cos_sin: Optional[torch.Tensor],
               rot_dims: int, k_scale: float, seq_lens=None, out_cache_loc=None, prefix_lens=None, extend_lens=None,
-              extend_start_loc=None) -> torch.Tensor:
+              extend_start_loc=None, in_act: Optional[str] = None) -> torch.Tensor:
     """Decayed linear attention over the per-request recurrent state (updated in place);
-    q / k [T, H·head_dim], v [T, H·v_dim] (row-strided views allowed) → o fp32 [T, H·v_dim]."""
+    q / k [T, H·head_dim], v [T, H·v_dim] (row-strided views allowed) → o fp32 [T, H·v_dim].  in_act "silu":
+    q, k and v are the SiLU of what is passed (applied in fp32 inside the kernel)."""
     _cuda(q, k, v, state, req_pool_indices, decay, cos_sin)
     T = q.shape[0]
     if state.dtype != torch.float32 or decay.dtype != torch.float32 or not state.is_contiguous():
@@ -941,8 +945,112 @@ def retention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Te
                             req_pool_indices.data_ptr(), _ptr(seq_lens), _ptr(out_cache_loc), _ptr(prefix_lens),
                             _ptr(extend_lens), _ptr(extend_start_loc), req_pool_indices.numel(), num_heads, head_dim,
                             v_dim, q.stride(0), k.stride(0), v.stride(0), decay.data_ptr(), _ptr(cos_sin), int(rot_dims),
-                            cos_sin.shape[0] if cos_sin is not None else 0, float(k_scale), _dta(q), _stream()),
+                            cos_sin.shape[0] if cos_sin is not None else 0, float(k_scale),
+                            {None: 0, "silu": 1}[in_act], _dta(q), _stream()),
           "spd_retention")
+    return o
+
+
+# ------------------------------------------------------------------------------------------------
+# a residual kept as several streams, rotary positions with biased projections, gated matrix memory
+# ------------------------------------------------------------------------------------------------
+def embed_norm_streams(table: torch.Tensor, idx: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+                       streams: int) -> torch.Tensor:
+    """fp32 [n, streams, dim]: every stream starts as the RMS-normed embedding row (weight None: the raw row)."""
+    _cuda(table, idx, weight)
+    if idx.dtype != torch.int64:
+        idx = idx.long()
+    if weight is not None and (weight.dtype != table.dtype or not weight.is_contiguous()):
+        raise RuntimeError("embed_norm_streams: the norm weight shares the table's dtype")
+    out = torch.empty((idx.numel(), int(streams), table.shape[1]), device=table.device, dtype=torch.float32)
+    check(lib.spd_embed_norm_streams(out.data_ptr(), table.data_ptr(), idx.data_ptr(), _ptr(weight), idx.numel(),
+                                     table.shape[1], table.shape[0], int(streams), float(eps), _dta(table), _stream()),
+          "spd_embed_norm_streams")
+    return out
+
+
+def streams_mix_norm(X: torch.Tensor, weight: Optional[torch.Tensor], eps: float, a: Optional[torch.Tensor] = None,
+                     b: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None, sa: float = 1.0,
+                     sb: float = 1.0, sbias: float = 1.0, mix: Optional[torch.Tensor] = None,
+                     out_w: Optional[torch.Tensor] = None, mult: float = 1.0, in_w: Optional[torch.Tensor] = None,
+                     rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """X fp32 [T, S, dim] in place.  With a: y = sa·a + sb·b + sbias·bias and X'[t] = Σ_s mix[s, t] X[s] + mult ·
+    out_w[t] · y.  With weight: → norm(Σ_s in_w[s] X'[s]) · weight in the weight's dtype (in_w None: the plain sum);
+    rows (int64) selects the tokens that are read (no write then)."""
+    _cuda(X, weight, a, b, bias, mix, out_w, in_w, rows)
+    if X.dtype != torch.float32 or not X.is_contiguous() or X.dim() != 3:
+        raise RuntimeError("streams_mix_norm: the streams are contiguous fp32 [T, S, dim]")
+    T, S, d = X.shape
+    ref = weight if weight is not None else a
+    for t in (a, b):
+        if t is not None and (not t.is_contiguous() or tuple(t.shape) != (T, d) or t.dtype != ref.dtype):
+            raise RuntimeError("streams_mix_norm: a / b are contiguous [T, dim] in one dtype")
+    for t, n in ((bias, d), (mix, S * S), (out_w, S), (in_w, S)):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.numel() != n):
+            raise RuntimeError("streams_mix_norm: bias and stream coefficients are contiguous fp32")
+    n_out = T if rows is None else rows.numel()
+    out = torch.empty((n_out, d), device=X.device, dtype=weight.dtype) if weight is not None else None
+    check(lib.spd_streams_mix_norm(_ptr(out), X.data_ptr(), _ptr(a), _ptr(b), _ptr(bias), float(sa), float(sb),
+                                   float(sbias), _ptr(mix), _ptr(out_w), float(mult), _ptr(in_w), _ptr(weight),
+                                   _ptr(rows), n_out, d, S, float(eps), _dta(ref), _stream()), "spd_streams_mix_norm")
+    return out
+
+
+def rotary_bias_store(q: torch.Tensor, k: torch.Tensor, v: Optional[torch.Tensor], q_bias: Optional[torch.Tensor],
+                      k_bias: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: Optional[torch.Tensor],
+                      loc: torch.Tensor, positions: torch.Tensor, cos_sin: Optional[torch.Tensor], rot_dims: int,
+                      num_q_heads: int, num_kv_heads: int, head_dim: int, v_dim: int) -> torch.Tensor:
+    """→ rotated q + q_bias [T, Hq·head_dim]; the rotated k + k_bias go to k_pool[loc], the values to v_pool[loc]:
+    v, or (v None) the biased keys before the rotation.  q / k / v may be row-strided views."""
+    _cuda(q, k, v, q_bias, k_bias, k_pool, v_pool, loc, positions, cos_sin)
+    T = q.shape[0]
+    if any(t is not None and t.stride(1) != 1 for t in (q, k, v)):
+        raise RuntimeError("rotary_bias_store: q / k / v need contiguous rows")
+    for t in (q_bias, k_bias, cos_sin):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise RuntimeError("rotary_bias_store: biases and the cos / sin table are contiguous fp32")
+    if loc.dtype != torch.int64 or positions.dtype != torch.int64:
+        raise RuntimeError("rotary_bias_store: loc and positions are int64")
+    if not k_pool.is_contiguous() or (v_pool is not None and not v_pool.is_contiguous()):
+        raise RuntimeError("rotary_bias_store: the pools are contiguous")
+    out = torch.empty((T, num_q_heads * head_dim), device=q.device, dtype=q.dtype)
+    check(lib.spd_rotary_bias_store(out.data_ptr(), q.data_ptr(), k.data_ptr(), _ptr(v), _ptr(q_bias), _ptr(k_bias),
+                                    k_pool.data_ptr(), _ptr(v_pool), loc.data_ptr(), positions.data_ptr(),
+                                    _ptr(cos_sin), int(rot_dims), cos_sin.shape[0] if cos_sin is not None else 0, T,
+                                    num_q_heads, num_kv_heads, head_dim, v_dim, q.stride(0), k.stride(0),
+                                    v.stride(0) if v is not None else 0, out.stride(0), _dta(q), _stream()),
+          "spd_rotary_bias_store")
+    return out
+
+
+def matrix_memory_vector_dim(num_heads: int, head_dim: int, v_dim: int) -> int:
+    """Floats per request of the vector state that matrix_memory keeps beside the matrix state."""
+    return int(lib.spd_matrix_memory_vector_dim(int(num_heads), int(head_dim), int(v_dim)))
+
+
+def matrix_memory(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tensor, zf: torch.Tensor,
+                  state: torch.Tensor, vec: torch.Tensor, req_pool_indices, num_heads: int, head_dim: int, v_dim: int,
+                  i_bias: Optional[torch.Tensor], f_bias: Optional[torch.Tensor], cap: float, q_scale: float,
+                  seq_lens=None, out_cache_loc=None, prefix_lens=None, extend_lens=None,
+                  extend_start_loc=None) -> torch.Tensor:
+    """Exponentially gated matrix memory over the per-request state (matrix state `state`, normaliser and running
+    maximum in `vec`, both updated in place); zi / zf [T, H] are the raw gate projections.  → o fp32 [T, H·v_dim]."""
+    _cuda(q, k, v, zi, zf, state, vec, req_pool_indices, i_bias, f_bias)
+    T = q.shape[0]
+    if state.dtype != torch.float32 or vec.dtype != torch.float32 or not state.is_contiguous() or vec.stride(1) != 1:
+        raise RuntimeError("matrix_memory: the states are fp32")
+    if any(t.stride(1) != 1 for t in (q, k, v, zi, zf)) or not (q.dtype == k.dtype == v.dtype == zi.dtype == zf.dtype):
+        raise RuntimeError("matrix_memory: q / k / v / zi / zf need contiguous rows and one dtype")
+    for t in (i_bias, f_bias):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != num_heads):
+            raise RuntimeError("matrix_memory: gate biases are fp32 [heads]")
+    o = torch.empty((T, num_heads * v_dim), device=q.device, dtype=torch.float32)
+    check(lib.spd_matrix_memory(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), zi.data_ptr(), zf.data_ptr(),
+                                state.data_ptr(), vec.data_ptr(), vec.stride(0), req_pool_indices.data_ptr(),
+                                _ptr(seq_lens), _ptr(out_cache_loc), _ptr(prefix_lens), _ptr(extend_lens),
+                                _ptr(extend_start_loc), req_pool_indices.numel(), num_heads, head_dim, v_dim,
+                                q.stride(0), k.stride(0), v.stride(0), zi.stride(0), zf.stride(0), _ptr(i_bias),
+                                _ptr(f_bias), float(cap), float(q_scale), _dta(q), _stream()), "spd_matrix_memory")
     return o
 
 

@@ -12,6 +12,7 @@ _MODELS: Dict[str, Tuple[str, str]] = {
     "deepseek_v2": ("deepseek_v2", "DeepseekV2ForCausalLM"),
     "rimidra": ("rimidra", "RimidraForCausalLM"),
     "nupovik": ("nupovik", "NupovikForCausalLM"),
+    "matepel": ("matepel", "MatepelForCausalLM"),
 }
 
 

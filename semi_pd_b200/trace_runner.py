@@ -35,6 +35,8 @@ def build_worker(model: str, dtype: str, max_tokens: int, max_requests: int, cud
     pool_tokens = -(-pool_tokens // DEFAULT_RUN_LEN) * DEFAULT_RUN_LEN
     ctx = max_tokens + 64
     cfg = get_model_config(model)
+    if ctx > cfg.max_position_embeddings:  # position tables are built for the longest request the pool can hold
+        cfg = get_model_config(model, max_position_embeddings=ctx)
     sa = ServerArgs(model_path=model, dtype=dtype, load_format="auto", max_total_tokens=pool_tokens,
                     # the request pool adds one spare slot to what is asked for
                     max_running_requests=max(max_requests - 1, 1), context_length=ctx,
