@@ -75,10 +75,10 @@ def parse_args():
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--tp-steps", type=int, default=3)
     ap.add_argument("--clocks-csv", type=str, default="", help="write the nvidia-smi samples of the run here")
-    ap.add_argument("--family", type=str, default="", choices=["", "rimidra", "nupovik"],
+    ap.add_argument("--family", type=str, default="", choices=["", "rimidra", "nupovik", "matepel"],
                     help="instead of the default workload: prefill / decode throughput and per-kernel rooflines of "
-                         "that model family beside Llama (and, for nupovik, Rimidra) at equal size "
-                         "(scripts/bench_rimidra.py, scripts/bench_nupovik.py)")
+                         "that model family beside Llama (and, for nupovik and matepel, Rimidra) at equal size "
+                         "(scripts/bench_rimidra.py, scripts/bench_nupovik.py, scripts/bench_matepel.py)")
     ap.add_argument("--family-sizes", type=str, default="s,m")
     return ap.parse_args()
 
