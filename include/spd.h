@@ -528,6 +528,60 @@ int spd_matrix_memory(float* o, const void* q, const void* k, const void* v, con
                       int64_t zi_stride, int64_t zf_stride, const float* i_bias, const float* f_bias, float cap,
                       float q_scale, int dtype, spd_stream_t stream);
 
+/* spd_attn_general with three more options.  softcap > 0: score <- softcap * tanh(score / softcap) after the
+ * scale and before the distance bias.  num_v_heads (0: num_kv_heads): the value pool has fewer heads than the
+ * key pool and key head g reads value head g mod num_v_heads (several attention maps over one set of values).
+ * v_slot_stride (0: num_v_heads * v_dim): elements between two slots of v_pool — with v_pool = k_pool,
+ * num_v_heads = 1 and v_slot_stride = head_dim, the values are the first v_dim columns of the key rows (a latent
+ * cache). */
+int spd_attn_general_ex(void* out, const void* q, const void* k_pool, const void* v_pool,
+                        const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
+                        const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                        int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                        int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
+                        float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
+                        int qtemp_every, int64_t max_extend_len, float softcap, int num_v_heads,
+                        int64_t v_slot_stride, int dtype, spd_stream_t stream);
+/* x[t, :] = table[idx[t], :] * scale + pair[row, :] (fp32) with row = (prev * mul_prev + idx[t] * mul_cur) mod
+ * buckets, or `buckets` (the table's last row) for the first token of a request; pair == NULL: no pair term.
+ * prev is the token before in the same request: the row before in the batch, or prev_state[slot] (int32
+ * [slots], slot = req_pool_indices[r]) for the first row of a portion that does not start at position 0;
+ * afterwards prev_state[slot] holds the request's last token of this batch.  Decode (seq_lens != NULL; rows
+ * with out_cache_loc == 0 are padding and leave the state alone) or ragged extend as spd_attn_general. */
+int spd_embed_pair(float* x, const void* table, const void* pair, const int64_t* idx, int32_t* prev_state,
+                   const int64_t* req_pool_indices, const int64_t* seq_lens, const int64_t* out_cache_loc,
+                   const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                   int64_t batch, int64_t tokens, int64_t dim, int64_t table_rows, float scale, int64_t buckets,
+                   int64_t mul_prev, int64_t mul_cur, int dtype, spd_stream_t stream);
+/* x (fp32 [*, dim], in place) += a + x0 + vec (a [*, dim] in dtype, x0 fp32 [*, dim], vec fp32 [dim]; each
+ * nullable), then out[r, :] = tanh(alpha * x[row, :]) * w + b in dtype (w, b [dim]; out, w, b all NULL: update
+ * only).  rows (int64 [n_rows], nullable) selects the rows that are normed; nothing is added then. */
+int spd_residual_tanh_norm(void* out, float* x, const void* a, const float* x0, const float* vec, const void* w,
+                           const void* b, const int64_t* rows, int64_t n_rows, int64_t dim, float alpha, int dtype,
+                           spd_stream_t stream);
+/* One strided piece of a rotary step: head h of token t is read at src + t * src_row + h * src_head (elements),
+ * bias (fp32 [heads * head_dim], nullable) is added, the first `rot` channels are rotated, and the head is
+ * written to dst + (to_pool ? loc[t] : t) * dst_row + h * dst_head. */
+typedef struct {
+  const void* src;
+  const float* bias;
+  void* dst;
+  int64_t src_row, dst_row;
+  int32_t heads, head_dim, rot, src_head, dst_head, to_pool;
+} spd_rotary_segment_t;
+/* Up to four segments in one launch.  cos_sin fp32 [max_positions, rot_max] = cos || sin (rot_max / 2 each) of
+ * position * f_i; a segment with rot < rot_max uses the first rot / 2 of both.  paired != 0: channel 2 i turns
+ * with 2 i + 1, else channel i with i + rot / 2: (u, v) -> (u cos - v sin, v cos + u sin). */
+int spd_rotary_segments(const spd_rotary_segment_t* segments, int num_segments, const int64_t* positions,
+                        const int64_t* loc, const float* cos_sin, int rot_max, int64_t max_positions, int paired,
+                        int64_t tokens, int dtype, spd_stream_t stream);
+/* out[t, h, c] = y * sigmoid(gate[t, h * vdim + c]) with y = a[t, h, c], or — a2 given (same strides as a) —
+ * y = d / sqrt(mean_c(d^2) + eps) * post, d = a - lambda * a2 (the difference of two attention maps at unit RMS
+ * per head). */
+int spd_heads_gate(void* out, const void* a, const void* a2, const void* gate, int64_t tokens, int heads, int vdim,
+                   int64_t a_stride, int64_t gate_stride, int64_t out_stride, float lambda, float eps, float post,
+                   int dtype, spd_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

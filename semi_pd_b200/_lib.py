@@ -134,6 +134,16 @@ SIGNATURES = {
         [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i64, _i64, _i64, _i64,
          _p, _p, _f, _f, _i, _p],
     ),
+    "spd_attn_general_ex": (
+        _i,
+        [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i, _i, _i, _i, _i64, _i64, _i64, _f, _i, _p, _p,
+         _f, _i, _i64, _f, _i, _i64, _i, _p],
+    ),
+    "spd_embed_pair": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _i64, _i64, _i64,
+                            _i, _p]),
+    "spd_residual_tanh_norm": (_i, [_p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, _i, _p]),
+    "spd_rotary_segments": (_i, [_p, _i, _p, _p, _p, _i, _i64, _i, _i64, _i, _p]),
+    "spd_heads_gate": (_i, [_p, _p, _p, _p, _i64, _i, _i, _i64, _i64, _i64, _f, _f, _f, _i, _p]),
     "spd_attn_prefill_simt": (
         _i,
         [_p, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i, _i, _i, _i64, _i64, _i64, _f, _i, _p],
@@ -143,6 +153,13 @@ SIGNATURES = {
         [_p, _p, _p, _p, _p, _p, _p, _i64, _i, _i, _i, _i64, _i64, _i64, _f, _i, _p, _i64, _p],
     ),
 }
+
+
+class RotarySegment(C.Structure):
+    """spd_rotary_segment_t of include/spd.h."""
+    _fields_ = [("src", _p), ("bias", _p), ("dst", _p), ("src_row", _i64), ("dst_row", _i64), ("heads", C.c_int32),
+                ("head_dim", C.c_int32), ("rot", C.c_int32), ("src_head", C.c_int32), ("dst_head", C.c_int32),
+                ("to_pool", C.c_int32)]
 
 
 def declared_functions(header_path: str = HEADER_PATH):

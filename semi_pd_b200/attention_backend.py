@@ -67,7 +67,8 @@ class RadixAttention:
                  layer_id: int, logit_cap: float = 0.0, v_head_dim: int = -1,
                  sliding_window_size: int = -1, is_cross_attention: bool = False, prefix: str = "",
                  sinks: Optional[torch.Tensor] = None, distance_slopes: Optional[torch.Tensor] = None,
-                 query_temperature: Optional[tuple] = None, general: bool = False):
+                 query_temperature: Optional[tuple] = None, general: bool = False, num_v_heads: int = 0,
+                 v_slot_stride: int = 0):
         self.tp_q_head_num = num_heads
         self.tp_k_head_num = num_kv_heads
         self.tp_v_head_num = num_kv_heads
@@ -87,6 +88,11 @@ class RadixAttention:
         self.sinks = sinks
         self.distance_slopes = distance_slopes
         self.query_temperature = query_temperature
+        # also the general kernel's: logit_cap (cap · tanh(score / cap)), value heads fewer than key heads (key head g
+        # reads value head g mod num_v_heads), a slot stride of the value pool (values inside wider rows)
+        self.num_v_heads = num_v_heads or num_kv_heads
+        self.v_slot_stride = v_slot_stride
+        self.tp_v_head_num = self.num_v_heads
         self.general = bool(general or sinks is not None or distance_slopes is not None or query_temperature
                             or self.sliding_window_size > 0 or self.v_head_dim != self.qk_head_dim)
         self.k_scale = None
@@ -168,7 +174,8 @@ class SpdAttnBackend(AttentionBackend):
         coef, every = layer.query_temperature or (0.0, 0)
         common = dict(num_q_heads=layer.tp_q_head_num, num_kv_heads=layer.tp_k_head_num, head_dim=layer.qk_head_dim,
                       v_dim=layer.v_head_dim, sm_scale=layer.scaling, window=layer.sliding_window_size,
-                      sinks=layer.sinks, slopes=layer.distance_slopes, qtemp_coef=coef, qtemp_every=every)
+                      sinks=layer.sinks, slopes=layer.distance_slopes, qtemp_coef=coef, qtemp_every=every,
+                      softcap=layer.logit_cap, num_v_heads=layer.num_v_heads, v_slot_stride=layer.v_slot_stride)
         r2t = forward_batch.req_to_token_pool.req_to_token
         if forward_batch.forward_mode.is_decode():
             return ops.attn_general(q, k_buf, v_buf, r2t, forward_batch.req_pool_indices,
@@ -231,6 +238,24 @@ class SpdAttnBackend(AttentionBackend):
         return ops.rotary_bias_store(q, k, v, q_bias, k_bias, k_buf, v_buf, forward_batch.out_cache_loc,
                                      forward_batch.positions, cos_sin, rot_dims, layer.tp_q_head_num,
                                      layer.tp_k_head_num, layer.qk_head_dim, layer.v_head_dim)
+
+    def forward_pair_embedding(self, table, input_ids, forward_batch: ForwardBatch, scale: float = 1.0, pair=None,
+                               buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0):
+        """Embedding rows times `scale` plus the row of a hashed (previous token, token) table; the previous token of
+        a portion's first row comes from (and the portion's last token goes to) the request's slot of the state
+        pool's `prev_token`.  → fp32 [T, dim]."""
+        if pair is None:
+            return ops.embed_pair(table, input_ids, scale)
+        rows = self._batch_rows(forward_batch)
+        return ops.embed_pair(table, input_ids, scale, pair=pair, buckets=buckets, mul_prev=mul_prev, mul_cur=mul_cur,
+                              prev_state=forward_batch.token_to_kv_pool.state_pool.prev_token,
+                              req_pool_indices=forward_batch.req_pool_indices, **rows)
+
+    def forward_rotary_segments(self, segments, forward_batch: ForwardBatch, cos_sin, dtype, paired: bool = False):
+        """Bias + partial rotation by the batch's positions of up to four strided segments in one launch; segments
+        made with to_pool=True are written at the batch's cache slots (ops.rotary_segment / rotary_segments)."""
+        ops.rotary_segments(segments, forward_batch.positions, cos_sin, dtype, loc=forward_batch.out_cache_loc,
+                            paired=paired)
 
     def forward_token_shift(self, h, mu, layer, forward_batch: ForwardBatch):
         """Token shift of a mixer's input: → [n_mix, T, dim] = h + (previous row − h) · mu[s]; the row before a

@@ -72,6 +72,12 @@ class ModelConfig:
     # multiplied by residual_mult before it is added
     num_streams: Optional[int] = None
     residual_mult: float = 1.0
+    # model_type "sugelix": the embedding row is multiplied by embedding_scale; pair_embedding {"buckets", "mul_prev",
+    # "mul_cur"} adds a row of a hashed (previous token, token) table (None: no such table); loop_times is how often
+    # the looped block runs (1: no loop) — each pass adds its row of a [loop_times, width] step table
+    embedding_scale: float = 1.0
+    pair_embedding: Optional[dict] = None
+    loop_times: int = 1
 
     @property
     def context_len(self) -> int:
@@ -144,6 +150,26 @@ def _rimidra_config(path: str, cfg: dict, **overrides) -> ModelConfig:
     return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "rimidra", **kw)
 
 
+def expand_loop(layers: List[dict], loop: Optional[dict]) -> List[dict]:
+    """Layer RUNS in execution order for a config whose block of layers [start, stop) is executed `times` times back
+    to back with the same tensors.  Every run is a copy of its layer's spec plus "layer" (the index in the
+    checkpoint's names), "weights_of" (the first run of the same layer; None for that run itself), "opens_pass"
+    (the first layer of every pass of the loop) and "pass_index" (the number of that pass, None elsewhere)."""
+    order = [(i, None) for i in range(len(layers))]
+    if loop is not None:
+        a, b, n = int(loop["start"]), int(loop["stop"]), int(loop["times"])
+        if not (0 <= a < b <= len(layers)) or n < 1:
+            raise ValueError(f"loop {loop} does not fit {len(layers)} layers")
+        order = order[:a] + [(i, t if i == a else None) for t in range(n) for i in range(a, b)] + order[b:]
+    runs, first = [], {}
+    for i, t in order:
+        spec = dict(layers[i])
+        spec.update(layer=i, opens_pass=t is not None, pass_index=t, weights_of=first.get(i))
+        first.setdefault(i, len(runs))
+        runs.append(spec)
+    return runs
+
+
 _NUPOVIK_MIXERS = ("gla", "latent_attention", "wkv")
 
 
@@ -160,19 +186,7 @@ def _nupovik_config(path: str, cfg: dict, **overrides) -> ModelConfig:
             raise ValueError(f"layer {i}: unknown mixer type {spec['type']!r}")
         if spec.get("mlp") is not None and spec["mlp"].get("kind") not in ("dense", "moe"):
             raise ValueError(f"layer {i}: unknown feed-forward kind {spec['mlp'].get('kind')!r}")
-    order = [(i, False) for i in range(len(layers))]
-    loop = cfg.get("loop") or None
-    if loop is not None:
-        a, b, n = int(loop["start"]), int(loop["stop"]), int(loop["times"])
-        if not (0 <= a < b <= len(layers)) or n < 1:
-            raise ValueError(f"loop {loop} does not fit {len(layers)} layers")
-        order = order[:a] + [(i, i == a) for _ in range(n) for i in range(a, b)] + order[b:]
-    runs, first = [], {}
-    for i, opens in order:
-        spec = dict(layers[i])
-        spec.update(layer=i, opens_pass=opens, weights_of=first.get(i))
-        first.setdefault(i, len(runs))
-        runs.append(spec)
+    runs = expand_loop(layers, cfg.get("loop") or None)
     heads = [int(s["mixer"]["heads"]) for s in runs]
     kw = dict(model_type="nupovik", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
               num_hidden_layers=len(runs), rms_norm_eps=float(cfg["norm"]["eps"]), layer_specs=runs,
@@ -228,8 +242,54 @@ def _matepel_config(path: str, cfg: dict, **overrides) -> ModelConfig:
     return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "matepel", **kw)
 
 
+_SUGELIX_MIXERS = ("attention", "attention_2", "latent_attention")
+
+
+def _sugelix_config(path: str, cfg: dict, **overrides) -> ModelConfig:
+    """config.json of the Sugelix family: {"architecture", "vocab", "width", "norm": {"eps"}, "embedding": {"scale",
+    "bigram": {"buckets", "mul_prev", "mul_cur"}}, "layers": [{"type", "mixer", "mlp"}, ...], "loop": {"start", "stop",
+    "times"}}.  Mixers: "attention" {heads, kv_heads, dim, vdim, scale, softcap, rot: {dims, base}} (rotation in
+    pairs), "attention_2" {heads, kv_heads, dim, vdim, scale, diff, mask: {size}, rot: {dims, base, scaling:
+    {factor}}} (two maps per head), "latent_attention" {heads, dim, rot_dim, vdim, q_rank, kv_rank, scale, mask:
+    {size}, rot: {base}}.  Feed-forward: {"kind": "moe", "router": {experts, top}, "expert": {ff, limit}, "shared":
+    {ff, limit} | null} or null.  `layer_specs` lists the layer RUNS (see expand_loop); every size and constant is
+    carried per layer."""
+    layers = cfg["layers"]
+    for i, spec in enumerate(layers):
+        if spec["type"] not in _SUGELIX_MIXERS:
+            raise ValueError(f"layer {i}: unknown mixer type {spec['type']!r}")
+        if spec.get("mlp") is not None and spec["mlp"].get("kind") != "moe":
+            raise ValueError(f"layer {i}: unknown feed-forward kind {spec['mlp'].get('kind')!r}")
+        m = spec["mixer"]
+        if spec["type"] != "latent_attention":
+            if int(m["heads"]) % int(m.get("kv_heads", m["heads"])):
+                raise ValueError(f"layer {i}: {m['heads']} heads are not a multiple of {m['kv_heads']} kv heads")
+            rot = int((m.get("rot") or {}).get("dims") or 0)
+            if rot % 2 or rot > int(m["dim"]):
+                raise ValueError(f"layer {i}: rot.dims {rot} must be even and at most dim {m['dim']}")
+        elif int(m["rot_dim"]) % 2:
+            raise ValueError(f"layer {i}: rot_dim {m['rot_dim']} must be even")
+    loop = cfg.get("loop") or None
+    runs = expand_loop(layers, loop)
+    emb = cfg.get("embedding") or {}
+    pair = emb.get("bigram") or None
+    kw = dict(model_type="sugelix", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+              num_hidden_layers=len(runs), rms_norm_eps=float(cfg["norm"]["eps"]), layer_specs=runs,
+              embedding_scale=float(emb.get("scale", 1.0)),
+              pair_embedding={k: int(pair[k]) for k in ("buckets", "mul_prev", "mul_cur")} if pair else None,
+              loop_times=int(loop["times"]) if loop else 1,
+              # summary fields other components print or size by; the per-layer values rule
+              num_attention_heads=max(int(s["mixer"]["heads"]) for s in runs),
+              num_key_value_heads=max(int(s["mixer"].get("kv_heads", 1)) for s in runs),
+              head_dim=max(int(s["mixer"]["dim"]) for s in runs), intermediate_size=0,
+              max_position_embeddings=int(cfg.get("context", 8192)))
+    kw.update(overrides)
+    return ModelConfig(name=os.path.basename(os.path.normpath(path)) or "sugelix", **kw)
+
+
 # config.json "architecture" -> reader
-_ARCHITECTURE_READERS = {"Rimidra": _rimidra_config, "Nupovik": _nupovik_config, "Matepel": _matepel_config}
+_ARCHITECTURE_READERS = {"Rimidra": _rimidra_config, "Nupovik": _nupovik_config, "Matepel": _matepel_config,
+                         "Sugelix": _sugelix_config}
 
 
 def load_model_config(path: str, **overrides) -> ModelConfig:

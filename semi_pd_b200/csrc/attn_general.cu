@@ -13,7 +13,7 @@
 namespace spd {
 
 constexpr int kGenMaxVPerLane = 16;  // v_dim <= 512: value columns a lane holds (instantiated for 8 and 16)
-constexpr int kGenMaxHeadDim = 512;
+constexpr int kGenMaxHeadDim = 1024;  // key rows may be wider than value rows (a latent with a rotated slice)
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ krow, int dk);
@@ -60,7 +60,7 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
                     const int32_t* __restrict__ extend_start_loc, int batch, int64_t total_tokens, int H, int G,
                     int dk, int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale,
                     int window, const float* __restrict__ sinks, const float* __restrict__ slopes, float qtemp_coef,
-                    int qtemp_every) {
+                    int qtemp_every, float softcap, int Gv, int64_t v_slot) {
   extern __shared__ float q_smem[];  // [4][dk]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   // item = h * tokens_padded + t with tokens_padded a multiple of 4: the warps of a CTA share a head
@@ -111,7 +111,9 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
     float s = -INFINITY;
     if (valid) {
       slot = page[j];
-      s = dot_row<T>(qs, k_pool + ((int64_t)slot * G + g) * dk, dk) - slope * (float)(pos - j);
+      s = dot_row<T>(qs, k_pool + ((int64_t)slot * G + g) * dk, dk);
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      s -= slope * (float)(pos - j);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);  // m = -inf (first tile, no sink): 0
@@ -124,7 +126,7 @@ attn_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __res
     for (int jj = 0; jj < n; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int sj = __shfl_sync(0xffffffffu, slot, jj);
-      const T* vrow = v_pool + ((int64_t)sj * G + g) * dv;
+      const T* vrow = v_pool + (int64_t)sj * v_slot + (int64_t)(g % Gv) * dv;
 #pragma unroll
       for (int i = 0; i < VMAX; ++i) {
         const int c = lane + 32 * i;
@@ -150,7 +152,8 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
                            const int64_t* __restrict__ req_pool_indices, const int64_t* __restrict__ seq_lens, int H,
                            int G, int dk, int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride,
                            float sm_scale, int window, const float* __restrict__ sinks,
-                           const float* __restrict__ slopes, float qtemp_coef, int qtemp_every) {
+                           const float* __restrict__ slopes, float qtemp_coef, int qtemp_every, float softcap, int Gv,
+                           int64_t v_slot) {
   extern __shared__ float dec_smem[];  // q [dk] | m [4] | l [4] | acc [4][dv]
   float* qs = dec_smem;
   float* sm_m = qs + dk;
@@ -180,7 +183,9 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
     float s = -INFINITY;
     if (valid) {
       slot = page[j];
-      s = dot_row<T>(qs, k_pool + ((int64_t)slot * G + g) * dk, dk) - slope * (float)(pos - j);
+      s = dot_row<T>(qs, k_pool + ((int64_t)slot * G + g) * dk, dk);
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      s -= slope * (float)(pos - j);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float corr = expf(m - m_new);
@@ -193,7 +198,7 @@ attn_general_decode_kernel(T* __restrict__ out, const T* __restrict__ q, const T
     for (int jj = 0; jj < n; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int sj = __shfl_sync(0xffffffffu, slot, jj);
-      const T* vrow = v_pool + ((int64_t)sj * G + g) * dv;
+      const T* vrow = v_pool + (int64_t)sj * v_slot + (int64_t)(g % Gv) * dv;
 #pragma unroll
       for (int i = 0; i < VMAX; ++i) {
         const int c = lane + 32 * i;
@@ -278,7 +283,8 @@ attn_general_decode_group_kernel(T* __restrict__ out, const T* __restrict__ q, c
                                  const int64_t* __restrict__ req_pool_indices, const int64_t* __restrict__ seq_lens,
                                  int H, int G, int dk, int64_t q_stride, int64_t out_stride, int64_t r2t_stride,
                                  float sm_scale, int window, const float* __restrict__ sinks,
-                                 const float* __restrict__ slopes, float qtemp_coef, int qtemp_every, int q_bytes) {
+                                 const float* __restrict__ slopes, float qtemp_coef, int qtemp_every, int q_bytes,
+                                 float softcap, int Gv, int64_t v_slot) {
   constexpr int N = 16 / (int)sizeof(T);
   constexpr int DV = 32 * VPL;
   constexpr int vstride = DV * (int)sizeof(T) + 16;
@@ -330,7 +336,7 @@ attn_general_decode_group_kernel(T* __restrict__ out, const T* __restrict__ q, c
       }
     if (lane < v_rows * vc)
       for (int kk = v_lrow; kk < n; kk += v_rows) {
-        const T* src = v_pool + ((int64_t)slots[kk] * G + g) * DV;
+        const T* src = v_pool + (int64_t)slots[kk] * v_slot + (int64_t)(g % Gv) * DV;
 #pragma unroll
         for (int ch = v_lch; ch < vc; ch += 32) cp_async16(smem_u32(vt + kk * vstride + ch * 16), src + ch * N, true);
       }
@@ -368,7 +374,8 @@ attn_general_decode_group_kernel(T* __restrict__ out, const T* __restrict__ q, c
     for (int rr = 0; rr < RMAX; ++rr) {
       p[rr] = 0.f;
       if (rr < R) {
-        const float sv = valid ? s[rr] - slope[rr] * dist : -INFINITY;
+        const float sc = softcap > 0.f ? softcap * tanhf(s[rr] / softcap) : s[rr];
+        const float sv = valid ? sc - slope[rr] * dist : -INFINITY;
         const float m_new = fmaxf(m[rr], warp_max(sv));  // finite: the tile has at least one key
         const float corr = expf(m[rr] - m_new);          // first tile (m = -inf): 0
         p[rr] = valid ? expf(sv - m_new) : 0.f;
@@ -434,7 +441,8 @@ int attn_general_decode_group_launch(size_t smem, int q_bytes, int64_t batch, cu
                                      const void* k_pool, const void* v_pool, const int32_t* req_to_token,
                                      const int64_t* req_pool_indices, const int64_t* seq_lens, int H, int G, int dk,
                                      int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
-                                     const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every) {
+                                     const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every,
+                                     float softcap, int Gv, int64_t v_slot) {
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     SPD_CUDA(cudaFuncSetAttribute(attn_general_decode_group_kernel<T, VPL, RMAX, NW>,
@@ -444,7 +452,7 @@ int attn_general_decode_group_launch(size_t smem, int q_bytes, int64_t batch, cu
   SPD_CUDA(launch(attn_general_decode_group_kernel<T, VPL, RMAX, NW>, dim3((unsigned)batch, (unsigned)G), dim3(NW * 32), smem,
                   stream, /*pdl=*/false, (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token,
                   req_pool_indices, seq_lens, H, G, dk, q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes,
-                  qtemp_coef, qtemp_every, q_bytes));
+                  qtemp_coef, qtemp_every, q_bytes, softcap, Gv, v_slot));
   return 0;
 }
 
@@ -463,14 +471,15 @@ int attn_general_mma_try(void* out, const void* q, const void* k_pool, const voi
                          const int64_t* req_pool_indices, const int32_t* prefix_lens, const int32_t* extend_lens,
                          const int32_t* extend_start_loc, int64_t batch, int64_t max_extend_len, int H, int G, int dk,
                          int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
-                         const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, int dtype,
-                         cudaStream_t stream);
+                         const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, float softcap,
+                         int Gv, int64_t v_slot, int dtype, cudaStream_t stream);
 
 int attn_general_mma_decode_try(void* out, const void* q, const void* k_pool, const void* v_pool,
                                 const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
                                 int64_t batch, int H, int G, int dk, int dv, int64_t q_stride, int64_t out_stride,
                                 int64_t r2t_stride, float sm_scale, int window, const float* sinks, const float* slopes,
-                                float qtemp_coef, int qtemp_every, int dtype, cudaStream_t stream);
+                                float qtemp_coef, int qtemp_every, float softcap, int Gv, int64_t v_slot, int dtype,
+                                cudaStream_t stream);
 
 }  // namespace spd
 
@@ -492,13 +501,20 @@ int spd_kv_store(const void* k, const void* v, void* k_pool, void* v_pool, const
   return 0;
 }
 
-int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v_pool,
-                     const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
-                     const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
-                     int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
-                     int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
-                     float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
-                     int qtemp_every, int64_t max_extend_len, int dtype, spd_stream_t stream) {
+int spd_attn_general_ex(void* out, const void* q, const void* k_pool, const void* v_pool,
+                        const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
+                        const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                        int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                        int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
+                        float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
+                        int qtemp_every, int64_t max_extend_len, float softcap, int num_v_heads,
+                        int64_t v_slot_stride, int dtype, spd_stream_t stream) {
+  if (num_v_heads <= 0) num_v_heads = num_kv_heads;
+  if (v_slot_stride <= 0) v_slot_stride = (int64_t)num_v_heads * v_dim;
+  const int Gv = num_v_heads;
+  const int64_t v_slot = v_slot_stride;
+  SPD_REQUIRE(num_kv_heads % num_v_heads == 0 && softcap >= 0.f, SPD_E_SHAPE,
+              "spd_attn_general: kv heads %d not a multiple of value heads %d", num_kv_heads, num_v_heads);
   SPD_REQUIRE(out && q && k_pool && v_pool && req_to_token && req_pool_indices, SPD_E_BADARG,
               "spd_attn_general: null pointer");
   SPD_REQUIRE(seq_lens != nullptr || (prefix_lens && extend_lens && extend_start_loc), SPD_E_BADARG,
@@ -516,7 +532,7 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
       const int rc = attn_general_mma_decode_try(out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens, batch,
                                                  num_q_heads, num_kv_heads, head_dim, v_dim, q_stride, out_stride,
                                                  req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef,
-                                                 qtemp_every, dtype, as_stream(stream));
+                                                 qtemp_every, softcap, Gv, v_slot, dtype, as_stream(stream));
       if (rc != 1) return rc;
     }
     // grouped form: 16-byte rows, v_dim 32 x {1, 2, 4, 8}, up to 8 query heads per key/value head
@@ -530,13 +546,13 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
     const size_t gsmem = (size_t)q_bytes + nw * per_warp;
     const bool grouped = (dtype == SPD_F32 || dtype == SPD_BF16) && R <= 8 && head_dim % (16 / (int)esz) == 0 &&
                          (v_dim == 32 || v_dim == 64 || v_dim == 128 || v_dim == 256) && aligned16(k_pool) &&
-                         aligned16(v_pool) && gsmem <= 200 * 1024 && num_kv_heads <= 65535 &&
+                         aligned16(v_pool) && v_slot % (16 / (int64_t)esz) == 0 && gsmem <= 200 * 1024 && num_kv_heads <= 65535 &&
                          getenv("SPD_ATTN_DECODE_PER_HEAD") == nullptr;
     if (grouped) {
 #define SPD_GRP_ARGS                                                                                                  \
   gsmem, q_bytes, batch, as_stream(stream), out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens,         \
       num_q_heads, num_kv_heads, head_dim, q_stride, out_stride, req_to_token_stride, sm_scale, window, sinks, slopes, \
-      qtemp_coef, qtemp_every
+      qtemp_coef, qtemp_every, softcap, Gv, v_slot
 #define SPD_GRP_R(TT, VPL)                                                                     \
   do {                                                                                         \
     if (R <= 1) return nw == 8 ? attn_general_decode_group_launch<TT, VPL, 1, 8>(SPD_GRP_ARGS)  \
@@ -567,7 +583,8 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
       SPD_CUDA(launch(kern, dim3((unsigned)batch, (unsigned)num_q_heads), dim3(128), dsmem,
                       as_stream(stream), /*pdl=*/false, (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool,
                       req_to_token, req_pool_indices, seq_lens, num_q_heads, num_kv_heads, head_dim, v_dim, q_stride,
-                      out_stride, req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every));
+                      out_stride, req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every, softcap,
+                      Gv, v_slot));
     });
     return 0;
   }
@@ -575,7 +592,7 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
     const int rc = attn_general_mma_try(out, q, k_pool, v_pool, req_to_token, req_pool_indices, prefix_lens, extend_lens,
                                         extend_start_loc, batch, max_extend_len, num_q_heads, num_kv_heads, head_dim,
                                         v_dim, q_stride, out_stride, req_to_token_stride, sm_scale, window, sinks, slopes,
-                                        qtemp_coef, qtemp_every, dtype, as_stream(stream));
+                                        qtemp_coef, qtemp_every, softcap, Gv, v_slot, dtype, as_stream(stream));
     if (rc != 1) return rc;
   }
   const int64_t tokens4 = (total_tokens + 3) / 4 * 4;
@@ -588,9 +605,22 @@ int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v
                     (T*)out, (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, seq_lens,
                     prefix_lens, extend_lens, extend_start_loc, (int)batch, total_tokens, num_q_heads, num_kv_heads,
                     head_dim, v_dim, q_stride, out_stride, req_to_token_stride, sm_scale, window, sinks, slopes,
-                    qtemp_coef, qtemp_every));
+                    qtemp_coef, qtemp_every, softcap, Gv, v_slot));
   });
   return 0;
+}
+
+int spd_attn_general(void* out, const void* q, const void* k_pool, const void* v_pool,
+                     const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
+                     const int32_t* prefix_lens, const int32_t* extend_lens, const int32_t* extend_start_loc,
+                     int64_t batch, int64_t total_tokens, int num_q_heads, int num_kv_heads, int head_dim,
+                     int v_dim, int64_t q_stride, int64_t out_stride, int64_t req_to_token_stride,
+                     float sm_scale, int window, const float* sinks, const float* slopes, float qtemp_coef,
+                     int qtemp_every, int64_t max_extend_len, int dtype, spd_stream_t stream) {
+  return spd_attn_general_ex(out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens, prefix_lens, extend_lens,
+                             extend_start_loc, batch, total_tokens, num_q_heads, num_kv_heads, head_dim, v_dim, q_stride,
+                             out_stride, req_to_token_stride, sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every,
+                             max_extend_len, 0.f, 0, 0, dtype, stream);
 }
 
 }  // extern "C"

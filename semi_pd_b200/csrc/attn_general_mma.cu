@@ -43,6 +43,13 @@ __device__ __forceinline__ void gm_ldsm_x4_trans(uint32_t (&r)[4], const void* p
                : "r"(smem_u32(p)));
 }
 
+// tanh for the score cap of the 16-bit kernels: 1 - 2 / (e^(2x) + 1) on the fast exponential and division (absolute
+// error of a few 1e-7; the argument is clamped where tanh is 1 to fp32 precision).  The 32-bit kernels call tanhf.
+__device__ __forceinline__ float gm_tanh(float x) {
+  x = fminf(fmaxf(x, -15.f), 15.f);
+  return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f);
+}
+
 template <typename T, int DK, int DV>
 __global__ void __launch_bounds__(kGmThreads)
 attn_general_mma_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_pool,
@@ -51,7 +58,7 @@ attn_general_mma_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
                         const int32_t* __restrict__ extend_lens, const int32_t* __restrict__ extend_start_loc, int H,
                         int G, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
                         const float* __restrict__ sinks, const float* __restrict__ slopes, float qtemp_coef,
-                        int qtemp_every) {
+                        int qtemp_every, float softcap, int Gv, int64_t v_slot) {
   constexpr int LDK = DK + 8, LDV = DV + 8;  // +16 B per row: ldmatrix rows fall into distinct banks
   extern __shared__ __align__(16) unsigned char gm_smem[];
   T* sQ = reinterpret_cast<T*>(gm_smem);   // [BQ][LDK]
@@ -88,7 +95,7 @@ attn_general_mma_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
       const int row = idx / (DV / 8), c = idx % (DV / 8);
       const bool ok = jb + row <= j_hi;
       const int64_t slot = ok ? page[jb + row] : 0;
-      cp_async16(smem_u32(sV + (buf * kGmBK + row) * LDV + c * 8), v_pool + (slot * G + g) * DV + c * 8, ok);
+      cp_async16(smem_u32(sV + (buf * kGmBK + row) * LDV + c * 8), v_pool + slot * v_slot + (int64_t)(g % Gv) * DV + c * 8, ok);
     }
   };
   load_kv(0, 0);
@@ -96,13 +103,15 @@ attn_general_mma_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
 
   const int rl[2] = {warp * 16 + (lane >> 2), warp * 16 + (lane >> 2) + 8};
   const int64_t pi[2] = {i0 + rl[0], i0 + rl[1]};
-  float sc[2];
+  float sc[2], scc[2];  // score multipliers into the exp2 domain, and (with a cap) into units of the cap
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
     float temp = 1.f;
     if (qtemp_every > 0) temp = 1.f + qtemp_coef * logf((float)((pi[x] + 1) / qtemp_every + 1));
+    scc[x] = softcap > 0.f ? sm_scale * temp / softcap : 0.f;
     sc[x] = sm_scale * temp * kLog2e;
   }
+  const float capl = softcap * kLog2e;
   const float sl = (slopes != nullptr ? slopes[h] : 0.f) * kLog2e;
   const float sink2 = sinks != nullptr ? sinks[h] * kLog2e : -INFINITY;
   float m[2] = {sink2, sink2}, l[2] = {0.f, 0.f};  // l: this thread's share of the row sum
@@ -149,7 +158,8 @@ attn_general_mma_kernel(T* __restrict__ out, const T* __restrict__ q, const T* _
         const int64_t j = jb + nb * 8 + (lane & 3) * 2 + (e & 1);
         const int64_t dist = pi[x] - j;
         const bool ok = dist >= 0 && (window <= 0 || dist < window) && pi[x] <= j_hi;
-        const float v = ok ? s[nb][e] * sc[x] - sl * (float)dist : -INFINITY;
+        const float z = softcap > 0.f ? capl * gm_tanh(s[nb][e] * scc[x]) : s[nb][e] * sc[x];
+        const float v = ok ? z - sl * (float)dist : -INFINITY;
         s[nb][e] = v;
         mx[x] = fmaxf(mx[x], v);
       }
@@ -215,7 +225,8 @@ static int gm_launch(void* out, const void* q, const void* k_pool, const void* v
                      const int64_t* req_pool_indices, const int32_t* prefix_lens, const int32_t* extend_lens,
                      const int32_t* extend_start_loc, int64_t batch, int64_t max_extend_len, int H, int G,
                      int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
-                     const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, cudaStream_t stream) {
+                     const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, float softcap, int Gv,
+                     int64_t v_slot, cudaStream_t stream) {
   constexpr size_t smem = sizeof(T) * ((size_t)kGmBQ * (DK + 8) + 2 * kGmBK * (DK + 8) + 2 * kGmBK * (DV + 8));
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -226,7 +237,7 @@ static int gm_launch(void* out, const void* q, const void* k_pool, const void* v
   SPD_CUDA(launch(attn_general_mma_kernel<T, DK, DV>, grid, dim3(kGmThreads), smem, stream, /*pdl=*/false, (T*)out,
                   (const T*)q, (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, prefix_lens,
                   extend_lens, extend_start_loc, H, G, q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes,
-                  qtemp_coef, qtemp_every));
+                  qtemp_coef, qtemp_every, softcap, Gv, v_slot));
   return 0;
 }
 
@@ -235,9 +246,10 @@ int attn_general_mma_try(void* out, const void* q, const void* k_pool, const voi
                          const int64_t* req_pool_indices, const int32_t* prefix_lens, const int32_t* extend_lens,
                          const int32_t* extend_start_loc, int64_t batch, int64_t max_extend_len, int H, int G, int dk,
                          int dv, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
-                         const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, int dtype,
-                         cudaStream_t stream) {
+                         const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, float softcap,
+                         int Gv, int64_t v_slot, int dtype, cudaStream_t stream) {
   if (dtype != SPD_BF16 && dtype != SPD_F16) return 1;
+  if (v_slot % 8 != 0) return 1;
   if (max_extend_len < 16 || batch > 65535 || H > 65535) return 1;  // short portions: the CUDA-core kernel
   if (q_stride % 8 != 0 || out_stride % 2 != 0 || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool) ||
       (reinterpret_cast<uintptr_t>(out) & 3u) != 0)
@@ -248,17 +260,18 @@ int attn_general_mma_try(void* out, const void* q, const void* k_pool, const voi
       return gm_launch<__nv_bfloat16, DKV, DVV>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, prefix_lens, \
                                                 extend_lens, extend_start_loc, batch, max_extend_len, H, G, q_stride, \
                                                 out_stride, r2t_stride, sm_scale, window, sinks, slopes, qtemp_coef, \
-                                                qtemp_every, stream);                                               \
+                                                qtemp_every, softcap, Gv, v_slot, stream);                          \
     return gm_launch<__half, DKV, DVV>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, prefix_lens,        \
                                        extend_lens, extend_start_loc, batch, max_extend_len, H, G, q_stride,        \
                                        out_stride, r2t_stride, sm_scale, window, sinks, slopes, qtemp_coef,         \
-                                       qtemp_every, stream);                                                        \
+                                       qtemp_every, softcap, Gv, v_slot, stream);                                   \
   }
   SPD_GM_CASE(32, 32)
   SPD_GM_CASE(64, 64)
   SPD_GM_CASE(64, 128)
   SPD_GM_CASE(128, 64)
   SPD_GM_CASE(128, 128)
+  SPD_GM_CASE(192, 128)
 #undef SPD_GM_CASE
   return 1;
 }
@@ -287,7 +300,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
                                const int64_t* __restrict__ req_pool_indices, const int64_t* __restrict__ seq_lens,
                                int H, int G, int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale,
                                int window, const float* __restrict__ sinks, const float* __restrict__ slopes,
-                               float qtemp_coef, int qtemp_every) {
+                               float qtemp_coef, int qtemp_every, float softcap, int Gv, int64_t v_slot) {
   constexpr int LDK = DK + 8, LDV = DV + 8;
   constexpr size_t kQBytes = sizeof(T) * 16 * LDK;
   constexpr size_t kWarpBytes = kGdWarpHdr + sizeof(T) * kGdTK * (LDK + LDV);
@@ -318,7 +331,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
   const int rr[2] = {lane >> 2, (lane >> 2) + 8};  // this thread's two rows (query heads of the group)
   float temp = 1.f;
   if (qtemp_every > 0) temp = 1.f + qtemp_coef * logf((float)((pos + 1) / qtemp_every + 1));
-  const float sc = sm_scale * temp * kLog2e;
+  const float sc = sm_scale * temp * kLog2e, scc = softcap > 0.f ? sm_scale * temp / softcap : 0.f, capl = softcap * kLog2e;
   float sl[2];
 #pragma unroll
   for (int x = 0; x < 2; ++x) sl[x] = (slopes != nullptr && rr[x] < R) ? slopes[h0 + rr[x]] * kLog2e : 0.f;
@@ -329,7 +342,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
 
-  constexpr int kc = DK / 8, vc = DV / 8;  // 16-byte chunks per row; both divide 32
+  constexpr int kc = DK / 8, vc = DV / 8;  // 16-byte chunks per row; vc divides 32, kc is at most 32
   const int64_t j_lo = window > 0 ? (pos - window + 1 > 0 ? pos - window + 1 : 0) : 0;
   const int n_split = gridDim.z;  // CTAs of the cluster that share this (request, head)
   for (int64_t j0 = j_lo + kGdTK * ((int64_t)blockIdx.z * NW + warp); j0 <= pos; j0 += (int64_t)kGdTK * NW * n_split) {
@@ -337,7 +350,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
     __syncwarp();  // the previous tile has been read
     if (lane < n) slots[lane] = page[j0 + lane];
     __syncwarp();
-    for (int row = lane / kc; row < kGdTK; row += 32 / kc) {
+    for (int row = lane / kc; row < kGdTK && lane < (32 / kc) * kc; row += 32 / kc) {  // (lanes past the last whole row idle)
       const bool ok = row < n;
       const int64_t slot = ok ? slots[row] : 0;
       cp_async16(smem_u32(sK + row * LDK + (lane % kc) * 8), k_pool + (slot * G + g) * DK + (lane % kc) * 8, ok);
@@ -345,7 +358,7 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
     for (int row = lane / vc; row < kGdTK; row += 32 / vc) {
       const bool ok = row < n;
       const int64_t slot = ok ? slots[row] : 0;
-      cp_async16(smem_u32(sV + row * LDV + (lane % vc) * 8), v_pool + (slot * G + g) * DV + (lane % vc) * 8, ok);
+      cp_async16(smem_u32(sV + row * LDV + (lane % vc) * 8), v_pool + slot * v_slot + (int64_t)(g % Gv) * DV + (lane % vc) * 8, ok);
     }
     cp_async_commit();
     cp_async_wait<0>();
@@ -375,7 +388,8 @@ attn_general_mma_decode_kernel(T* __restrict__ out, const T* __restrict__ q, con
       for (int e = 0; e < 4; ++e) {
         const int x = e >> 1;
         const int col = nb * 8 + (lane & 3) * 2 + (e & 1);
-        const float v = col < n ? s[nb][e] * sc - sl[x] * (float)(pos - (j0 + col)) : -INFINITY;
+        const float z = softcap > 0.f ? capl * gm_tanh(s[nb][e] * scc) : s[nb][e] * sc;
+        const float v = col < n ? z - sl[x] * (float)(pos - (j0 + col)) : -INFINITY;
         s[nb][e] = v;
         mx[x] = fmaxf(mx[x], v);
       }
@@ -512,7 +526,8 @@ template <typename T, int DK, int DV, int NW>
 static int gd_launch_nw(void* out, const void* q, const void* k_pool, const void* v_pool, const int32_t* req_to_token,
                         const int64_t* req_pool_indices, const int64_t* seq_lens, int64_t batch, int H, int G,
                         int64_t q_stride, int64_t out_stride, int64_t r2t_stride, float sm_scale, int window,
-                        const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, cudaStream_t stream) {
+                        const float* sinks, const float* slopes, float qtemp_coef, int qtemp_every, float softcap, int Gv,
+                        int64_t v_slot, cudaStream_t stream) {
   constexpr size_t tiles = (size_t)NW * (kGdWarpHdr + sizeof(T) * kGdTK * (DK + 8 + DV + 8));
   constexpr size_t merge = sizeof(float) * (NW + 1) * 16 * (DV + 2);  // the warps' triples + the CTA's own
   constexpr size_t smem = sizeof(T) * 16 * (DK + 8) + (tiles > merge ? tiles : merge);
@@ -546,7 +561,7 @@ static int gd_launch_nw(void* out, const void* q, const void* k_pool, const void
   SPD_CUDA(cudaLaunchKernelEx(&cfg, attn_general_mma_decode_kernel<T, DK, DV, NW>, (T*)out, (const T*)q,
                               (const T*)k_pool, (const T*)v_pool, req_to_token, req_pool_indices, seq_lens, H, G,
                               q_stride, out_stride, r2t_stride, sm_scale, window, sinks, slopes, qtemp_coef,
-                              qtemp_every));
+                              qtemp_every, softcap, Gv, v_slot));
   return 0;
 }
 
@@ -555,8 +570,10 @@ int attn_general_mma_decode_try(void* out, const void* q, const void* k_pool, co
                                 const int32_t* req_to_token, const int64_t* req_pool_indices, const int64_t* seq_lens,
                                 int64_t batch, int H, int G, int dk, int dv, int64_t q_stride, int64_t out_stride,
                                 int64_t r2t_stride, float sm_scale, int window, const float* sinks, const float* slopes,
-                                float qtemp_coef, int qtemp_every, int dtype, cudaStream_t stream) {
+                                float qtemp_coef, int qtemp_every, float softcap, int Gv, int64_t v_slot, int dtype,
+                                cudaStream_t stream) {
   if (dtype != SPD_BF16 && dtype != SPD_F16) return 1;
+  if (v_slot % 8 != 0) return 1;
   if ((int64_t)G * ((H / G + 15) / 16) > 65535 || batch >= (1ll << 31)) return 1;
   if (q_stride % 8 != 0 || !aligned16(q) || !aligned16(k_pool) || !aligned16(v_pool)) return 1;
   // short windows do not fill eight warps: four warps then leave room for more CTAs per SM
@@ -567,23 +584,24 @@ int attn_general_mma_decode_try(void* out, const void* q, const void* k_pool, co
       return wide ? gd_launch_nw<__nv_bfloat16, DKV, DVV, 8>(out, q, k_pool, v_pool, req_to_token, req_pool_indices,  \
                                                              seq_lens, batch, H, G, q_stride, out_stride, r2t_stride, \
                                                              sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every, \
-                                                             stream)                                                  \
+                                                             softcap, Gv, v_slot, stream)                                                  \
                   : gd_launch_nw<__nv_bfloat16, DKV, DVV, 4>(out, q, k_pool, v_pool, req_to_token, req_pool_indices,  \
                                                              seq_lens, batch, H, G, q_stride, out_stride, r2t_stride, \
                                                              sm_scale, window, sinks, slopes, qtemp_coef, qtemp_every, \
-                                                             stream);                                                 \
+                                                             softcap, Gv, v_slot, stream);                                                 \
     return wide ? gd_launch_nw<__half, DKV, DVV, 8>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens, \
                                                     batch, H, G, q_stride, out_stride, r2t_stride, sm_scale, window,  \
-                                                    sinks, slopes, qtemp_coef, qtemp_every, stream)                   \
+                                                    sinks, slopes, qtemp_coef, qtemp_every, softcap, Gv, v_slot, stream)                   \
                 : gd_launch_nw<__half, DKV, DVV, 4>(out, q, k_pool, v_pool, req_to_token, req_pool_indices, seq_lens, \
                                                     batch, H, G, q_stride, out_stride, r2t_stride, sm_scale, window,  \
-                                                    sinks, slopes, qtemp_coef, qtemp_every, stream);                  \
+                                                    sinks, slopes, qtemp_coef, qtemp_every, softcap, Gv, v_slot, stream);                  \
   }
   SPD_GD_CASE(32, 32)
   SPD_GD_CASE(64, 64)
   SPD_GD_CASE(64, 128)
   SPD_GD_CASE(128, 64)
   SPD_GD_CASE(128, 128)
+  SPD_GD_CASE(192, 128)
 #undef SPD_GD_CASE
   return 1;
 }

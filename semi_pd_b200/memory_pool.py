@@ -387,10 +387,11 @@ class RecurrentStatePool:
     0 ignores what the slot held before (no clearing on reuse).  `layer_shapes[l]` is (heads,
     head_dim, v_dim) or None for layers without state.  `shift_dims[l]` (optional) is the row size of
     a second, vector-valued state of layer l — the previous token's mixer input of a token-shift
-    mixer, `shift[l]` fp32 [slots, dim] — or None."""
+    mixer, `shift[l]` fp32 [slots, dim] — or None.  `token_state`: the pool also keeps every request's last
+    token id (`prev_token` int32 [slots]) for an embedding that looks at pairs of tokens."""
 
     def __init__(self, num_slots: int, layer_shapes: Sequence[Optional[Tuple[int, int, int]]], device: str,
-                 shift_dims: Optional[Sequence[Optional[int]]] = None):
+                 shift_dims: Optional[Sequence[Optional[int]]] = None, token_state: bool = False):
         self.num_slots = num_slots
         self.layer_shapes = list(layer_shapes)
         self.shift_dims = list(shift_dims) if shift_dims is not None else [None] * len(self.layer_shapes)
@@ -401,6 +402,8 @@ class RecurrentStatePool:
         self.shift: List[Optional[torch.Tensor]] = [
             torch.zeros((num_slots, int(d)), dtype=torch.float32, device=device) if d else None
             for d in self.shift_dims]
+        self.prev_token: Optional[torch.Tensor] = (
+            torch.zeros((num_slots,), dtype=torch.int32, device=device) if token_state else None)
 
     @staticmethod
     def bytes_per_slot(layer_shapes: Sequence[Optional[Tuple[int, int, int]]],
@@ -419,7 +422,8 @@ class HybridTokenToKVPool(KVCache):
     """KV pool of a model whose layers differ: layer l with `layer_shapes[l]` = (kv_heads, k_dim,
     v_dim) owns k_buffer[l] [size + 1, kv_heads, k_dim] and v_buffer[l] [size + 1, kv_heads, v_dim]
     (key and value sizes may differ; v_dim 0: values are read from the key rows themselves — one
-    latent buffer, `v_buffer[l] is k_buffer[l]`); layers with None (recurrent mixers) own nothing here.  All
+    latent buffer, `v_buffer[l] is k_buffer[l]`; a fourth entry v_heads gives the values fewer heads than the
+    keys: several attention maps over one set of values); layers with None (recurrent mixers) own nothing here.  All
     layers share the slot ids of one TokenToKVPoolAllocator, as in MHATokenToKVPool.  `dtype` may be
     float32.  The recurrent layers' state pool travels with this object (`state_pool`), so both
     workers of a GPU see it through the one pool they already share."""
@@ -443,12 +447,12 @@ class HybridTokenToKVPool(KVCache):
         for s in self.layer_shapes:
             self.k_buffer.append(torch.zeros((rows, s[0], s[1]), dtype=dtype, device=device) if s else None)
             self.v_buffer.append(None if not s else self.k_buffer[-1] if s[2] == 0 else
-                                 torch.zeros((rows, s[0], s[2]), dtype=dtype, device=device))
+                                 torch.zeros((rows, s[3] if len(s) > 3 else s[0], s[2]), dtype=dtype, device=device))
 
     @staticmethod
     def bytes_per_token(layer_shapes, dtype: torch.dtype) -> int:
         esz = torch.empty((), dtype=dtype).element_size()
-        return sum(s[0] * (s[1] + s[2]) * esz for s in layer_shapes if s is not None)
+        return sum((s[0] * s[1] + (s[3] if len(s) > 3 else s[0]) * s[2]) * esz for s in layer_shapes if s is not None)
 
     def get_kv_size_bytes(self):
         k = sum(b.numel() * b.element_size() for b in self.k_buffer if b is not None)

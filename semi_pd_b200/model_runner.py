@@ -143,7 +143,7 @@ class ModelRunner:
             max_num_reqs = min(max(int(self.max_total_num_tokens / cfg.context_len * 512), 2048), 4096)
             if hybrid:
                 # every request slot owns a recurrent state: keep the state pool within a tenth of the device
-                per = RecurrentStatePool.bytes_per_slot(*self.model.cache_shapes()[1:])
+                per = RecurrentStatePool.bytes_per_slot(*self.model.cache_shapes()[1:3])
                 if per:
                     total = torch.cuda.mem_get_info(self.device)[1]
                     max_num_reqs = max(1, min(max_num_reqs, int(0.1 * total // per) - 1))
@@ -151,13 +151,15 @@ class ModelRunner:
         self.req_to_token_pool = ReqToTokenPool(size=max_num_reqs + 1, max_context_len=ctx + 4,
                                                 device=self.device)
         if hybrid:
-            # (kv shapes, matrix-state shapes[, vector-state sizes]) per layer
-            kv_shapes, state_shapes, *shift_dims = self.model.cache_shapes()
+            # (kv shapes, matrix-state shapes[, vector-state sizes[, {"token_state": bool}]]) per layer
+            kv_shapes, state_shapes, *more = self.model.cache_shapes()
+            extras = more[1] if len(more) > 1 else {}
             self.token_to_kv_pool = HybridTokenToKVPool(
                 self.max_total_num_tokens, page_size=1, dtype=self.kv_cache_dtype, layer_shapes=kv_shapes,
                 device=self.device,
                 state_pool=RecurrentStatePool(max_num_reqs + 1, state_shapes, device=self.device,
-                                              shift_dims=shift_dims[0] if shift_dims else None))
+                                              shift_dims=more[0] if more else None,
+                                              token_state=bool(extras.get("token_state"))))
         elif getattr(cfg, "model_type", "llama") == "deepseek_v2":
             self.token_to_kv_pool = MLATokenToKVPool(
                 self.max_total_num_tokens, page_size=1, dtype=self.kv_cache_dtype, kv_lora_rank=cfg.kv_lora_rank,

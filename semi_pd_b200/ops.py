@@ -729,19 +729,29 @@ def residual_rmsnorm2(x: torch.Tensor, weight: torch.Tensor, weight2: Optional[t
     return out, out2
 
 
-def linear_block_diag_any(x: torch.Tensor, weight: torch.Tensor, num_groups: int, k: int, n: int) -> torch.Tensor:
+def linear_block_diag_any(x: torch.Tensor, weight: torch.Tensor, num_groups: int, k: int, n: int,
+                          x_group_stride: Optional[int] = None, out: Optional[torch.Tensor] = None,
+                          out_group_stride: Optional[int] = None) -> torch.Tensor:
     """out[:, g n : (g + 1) n] = x[:, g k : (g + 1) k] @ weight[g n : (g + 1) n, :k].T for g < num_groups — the
-    per-head products of an absorbed latent attention; tensor cores where the shapes tile, CUDA cores otherwise."""
-    _cuda(x, weight)
+    per-head products of an absorbed latent attention; tensor cores where the shapes tile, CUDA cores otherwise.
+    x_group_stride / out_group_stride (default k / n): columns between two groups of x / out, for heads that carry
+    more than the multiplied slice; `out` is then a caller's [M, >= num_groups · out_group_stride] buffer."""
+    _cuda(x, weight, out)
     if x.dim() != 2 or weight.dim() != 2 or x.stride(1) != 1 or weight.stride(1) != 1 or x.dtype != weight.dtype:
         raise RuntimeError("linear_block_diag_any: x and weight must be 2-D, contiguous rows, same dtype")
-    if (x.dtype in _DTYPE and n % 128 == 0 and k % 64 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
-            and weight.data_ptr() % 16 == 0 and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc"):
-        return linear_block_diag(x, weight, num_groups, k, n, x_group_stride=k, out_group_stride=n)
+    xg = k if x_group_stride is None else int(x_group_stride)
+    og = n if out_group_stride is None else int(out_group_stride)
     M = x.shape[0]
-    out = torch.empty((M, num_groups * n), device=x.device, dtype=x.dtype)
+    if out is None:
+        out = torch.empty((M, num_groups * og), device=x.device, dtype=x.dtype)
+    elif out.dtype != x.dtype or out.stride(1) != 1 or out.shape[0] != M:
+        raise RuntimeError("linear_block_diag_any: out is [M, ...] with contiguous rows in x's dtype")
+    if (x.dtype in _DTYPE and n % 128 == 0 and k % 64 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0 and xg % 8 == 0 and og % 8 == 0 and out.stride(0) % 8 == 0
+            and out.data_ptr() % 16 == 0 and os.environ.get("SPD_HYBRID_GEMM", "tc") == "tc"):
+        return linear_block_diag(x, weight, num_groups, k, n, x_group_stride=xg, out=out, out_group_stride=og)
     check(lib.spd_linear_simt_block_diag(out.data_ptr(), x.data_ptr(), weight.data_ptr(), M, n, k, x.stride(0),
-                                         weight.stride(0), out.stride(0), num_groups, k, n, _dta(x), _stream()),
+                                         weight.stride(0), out.stride(0), num_groups, xg, og, _dta(x), _stream()),
           "spd_linear_simt_block_diag")
     return out
 
@@ -901,10 +911,14 @@ def attn_general(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, re
                  num_q_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, sm_scale: float, window: int = -1,
                  sinks: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None, qtemp_coef: float = 0.0,
                  qtemp_every: int = 0, seq_lens=None, prefix_lens=None, extend_lens=None, extend_start_loc=None,
-                 max_extend_len: int = 0) -> torch.Tensor:
+                 max_extend_len: int = 0, softcap: float = 0.0, num_v_heads: int = 0,
+                 v_slot_stride: int = 0) -> torch.Tensor:
     """Windowed / sink / distance-biased softmax attention over the paged pool; decode (seq_lens) or
     ragged extend (prefix_lens, extend_lens, extend_start_loc).  q [T, H·head_dim] → [T, H·v_dim].
-    max_extend_len > 0 (a host-side bound of extend_lens) lets 16-bit prefill run on the tensor cores."""
+    max_extend_len > 0 (a host-side bound of extend_lens) lets 16-bit prefill run on the tensor cores.
+    softcap > 0 caps the scaled scores by softcap · tanh(· / softcap); num_v_heads < num_kv_heads: key head g
+    reads value head g mod num_v_heads; v_slot_stride: elements between two slots of v_pool (values that are
+    the first v_dim columns of wider rows)."""
     _cuda(q, k_pool, v_pool, req_to_token, req_pool_indices, sinks, slopes)
     T = q.shape[0]
     if q.dim() != 2 or q.stride(1) != 1:
@@ -918,12 +932,13 @@ def attn_general(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, re
         if t is not None and t.dtype != torch.float32:
             raise RuntimeError("attn_general: sinks and slopes are fp32")
     out = torch.empty((T, num_q_heads * v_dim), device=q.device, dtype=q.dtype)
-    check(lib.spd_attn_general(out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
-                               req_to_token.data_ptr(), req_pool_indices.data_ptr(), _ptr(seq_lens), _ptr(prefix_lens),
-                               _ptr(extend_lens), _ptr(extend_start_loc), req_pool_indices.numel(), T, num_q_heads,
-                               num_kv_heads, head_dim, v_dim, q.stride(0), out.stride(0), req_to_token.stride(0),
-                               float(sm_scale), int(window), _ptr(sinks), _ptr(slopes), float(qtemp_coef),
-                               int(qtemp_every), int(max_extend_len), _dta(q), _stream()), "spd_attn_general")
+    check(lib.spd_attn_general_ex(out.data_ptr(), q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+                                  req_to_token.data_ptr(), req_pool_indices.data_ptr(), _ptr(seq_lens), _ptr(prefix_lens),
+                                  _ptr(extend_lens), _ptr(extend_start_loc), req_pool_indices.numel(), T, num_q_heads,
+                                  num_kv_heads, head_dim, v_dim, q.stride(0), out.stride(0), req_to_token.stride(0),
+                                  float(sm_scale), int(window), _ptr(sinks), _ptr(slopes), float(qtemp_coef),
+                                  int(qtemp_every), int(max_extend_len), float(softcap or 0.0), int(num_v_heads),
+                                  int(v_slot_stride), _dta(q), _stream()), "spd_attn_general")
     return out
 
 
@@ -1052,6 +1067,118 @@ def matrix_memory(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.T
                                 q.stride(0), k.stride(0), v.stride(0), zi.stride(0), zf.stride(0), _ptr(i_bias),
                                 _ptr(f_bias), float(cap), float(q_scale), _dta(q), _stream()), "spd_matrix_memory")
     return o
+
+
+# ------------------------------------------------------------------------------------------------
+# token-pair embedding, tanh norm, rotary positions over strided segments, gated attention heads
+# ------------------------------------------------------------------------------------------------
+def embed_pair(table: torch.Tensor, idx: torch.Tensor, scale: float = 1.0, pair: Optional[torch.Tensor] = None,
+               buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0, prev_state: Optional[torch.Tensor] = None,
+               req_pool_indices=None, seq_lens=None, out_cache_loc=None, prefix_lens=None, extend_lens=None,
+               extend_start_loc=None) -> torch.Tensor:
+    """fp32 [n, dim] = table[idx] · scale + pair[(prev · mul_prev + idx · mul_cur) mod buckets] (row `buckets` for a
+    request's first token).  prev: the row before of the same request, or prev_state[slot] (int32 [slots]) where a
+    portion starts; prev_state[slot] then receives the request's last token.  Decode (seq_lens) or ragged extend."""
+    _cuda(table, idx, pair, prev_state, req_pool_indices)
+    if idx.dtype != torch.int64:
+        idx = idx.long()
+    if pair is not None:
+        if pair.dtype != table.dtype or not pair.is_contiguous() or pair.shape[1] != table.shape[1] \
+                or pair.shape[0] != buckets + 1:
+            raise RuntimeError("embed_pair: the pair table is [buckets + 1, dim] in the table's dtype")
+        if prev_state is None or prev_state.dtype != torch.int32 or not prev_state.is_contiguous():
+            raise RuntimeError("embed_pair: the previous-token state is contiguous int32 [slots]")
+        if req_pool_indices.dtype != torch.int64 or (seq_lens is not None and seq_lens.dtype != torch.int64):
+            raise RuntimeError("embed_pair: req_pool_indices and seq_lens must be int64")
+        for t in (prefix_lens, extend_lens, extend_start_loc):
+            if t is not None and t.dtype != torch.int32:
+                raise RuntimeError("embed_pair: prefix_lens / extend_lens / extend_start_loc must be int32")
+    n = idx.numel()
+    out = torch.empty((n, table.shape[1]), device=table.device, dtype=torch.float32)
+    batch = req_pool_indices.numel() if req_pool_indices is not None else 0
+    check(lib.spd_embed_pair(out.data_ptr(), table.data_ptr(), _ptr(pair), idx.data_ptr(), _ptr(prev_state),
+                             _ptr(req_pool_indices), _ptr(seq_lens), _ptr(out_cache_loc), _ptr(prefix_lens),
+                             _ptr(extend_lens), _ptr(extend_start_loc), batch, n, table.shape[1], table.shape[0],
+                             float(scale), int(buckets), int(mul_prev), int(mul_cur), _dta(table), _stream()),
+          "spd_embed_pair")
+    return out
+
+
+def residual_tanh_norm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], alpha: float,
+                       a: Optional[torch.Tensor] = None, x0: Optional[torch.Tensor] = None,
+                       vec: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """x (fp32, in place) += a + x0 + vec (each optional); → tanh(alpha · x) · weight + bias in the weight's dtype
+    (None when weight is None: update only).  rows (int64) selects the rows that are normed (nothing is added)."""
+    _cuda(x, weight, bias, a, x0, vec, rows)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2:
+        raise RuntimeError("residual_tanh_norm: the residual stream is contiguous fp32 [T, dim]")
+    d = x.shape[1]
+    if a is not None and (not a.is_contiguous() or a.shape != x.shape or (weight is not None and a.dtype != weight.dtype)):
+        raise RuntimeError("residual_tanh_norm: a matches x, is contiguous and shares the weight's dtype")
+    for t, shape in ((x0, tuple(x.shape)), (vec, (d,))):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != shape):
+            raise RuntimeError("residual_tanh_norm: x0 [T, dim] and vec [dim] are contiguous fp32")
+    if (weight is None) != (bias is None) or (weight is not None and (weight.dtype != bias.dtype or weight.numel() != d
+                                                                       or bias.numel() != d)):
+        raise RuntimeError("residual_tanh_norm: weight and bias are [dim] in one dtype")
+    ref = weight if weight is not None else a
+    if ref is None:  # nothing but fp32 terms to add
+        ref = x
+    n = x.shape[0] if rows is None else rows.numel()
+    out = torch.empty((n, d), device=x.device, dtype=weight.dtype) if weight is not None else None
+    check(lib.spd_residual_tanh_norm(_ptr(out), x.data_ptr(), _ptr(a), _ptr(x0), _ptr(vec), _ptr(weight), _ptr(bias),
+                                     _ptr(rows), n, d, float(alpha), _dta(ref), _stream()), "spd_residual_tanh_norm")
+    return out
+
+
+def rotary_segment(src: torch.Tensor, dst: torch.Tensor, heads: int, head_dim: int, rot: int = 0,
+                   bias: Optional[torch.Tensor] = None, src_head: Optional[int] = None, dst_head: Optional[int] = None,
+                   to_pool: bool = False) -> _lib.RotarySegment:
+    """One piece of rotary_segments: src / dst are 2-D views whose first element is the first head's first channel
+    (row stride = stride(0); src_head / dst_head default to head_dim)."""
+    _cuda(src, dst, bias)
+    if src.stride(-1) != 1 or dst.stride(-1) != 1 or src.dtype != dst.dtype:
+        raise RuntimeError("rotary_segment: src and dst have contiguous rows and one dtype")
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != heads * head_dim):
+        raise RuntimeError("rotary_segment: bias is contiguous fp32 [heads * head_dim]")
+    seg = _lib.RotarySegment(src.data_ptr(), _ptr(bias), dst.data_ptr(), src.stride(0), dst.stride(0), heads, head_dim, rot,
+                             head_dim if src_head is None else src_head, head_dim if dst_head is None else dst_head,
+                             1 if to_pool else 0)
+    seg.keep = (src, dst, bias)  # the descriptor holds raw pointers: the tensors live as long as it does
+    return seg
+
+
+def rotary_segments(segments, positions: torch.Tensor, cos_sin: Optional[torch.Tensor], dtype: torch.dtype,
+                    loc: Optional[torch.Tensor] = None, paired: bool = False) -> None:
+    """Bias + partial rotation + scatter of up to four strided segments in one launch (see rotary_segment).
+    cos_sin fp32 [positions, rot_max] = cos ‖ sin; paired: channel 2 i turns with 2 i + 1, else i with i + rot / 2."""
+    _cuda(positions, cos_sin, loc)
+    if positions.dtype != torch.int64 or (loc is not None and loc.dtype != torch.int64):
+        raise RuntimeError("rotary_segments: positions and loc are int64")
+    if cos_sin is not None and (cos_sin.dtype != torch.float32 or not cos_sin.is_contiguous()):
+        raise RuntimeError("rotary_segments: the cos / sin table is contiguous fp32")
+    arr = (_lib.RotarySegment * len(segments))(*segments)
+    check(lib.spd_rotary_segments(arr, len(segments), positions.data_ptr(), _ptr(loc), _ptr(cos_sin),
+                                  cos_sin.shape[1] if cos_sin is not None else 0,
+                                  cos_sin.shape[0] if cos_sin is not None else 0, 1 if paired else 0,
+                                  positions.numel(), _DTYPE_ANY[dtype], _stream()), "spd_rotary_segments")
+
+
+def heads_gate(a: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int, a2: Optional[torch.Tensor] = None,
+               lam: float = 0.0, eps: float = 0.0, post: float = 1.0) -> torch.Tensor:
+    """[T, heads·vdim] = y · sigmoid(gate) with y = a, or (a2 given, a view with a's strides) the unit-RMS per head of
+    a − lam · a2 times post.  a / a2 / gate may be row-strided views."""
+    _cuda(a, a2, gate)
+    if a.stride(1) != 1 or gate.stride(1) != 1 or a.dtype != gate.dtype:
+        raise RuntimeError("heads_gate: a and gate need contiguous rows and one dtype")
+    if a2 is not None and (a2.stride(0) != a.stride(0) or a2.stride(1) != 1 or a2.dtype != a.dtype):
+        raise RuntimeError("heads_gate: a2 shares a's strides and dtype")
+    T = a.shape[0]
+    out = torch.empty((T, heads * vdim), device=a.device, dtype=a.dtype)
+    check(lib.spd_heads_gate(out.data_ptr(), a.data_ptr(), _ptr(a2), gate.data_ptr(), T, heads, vdim, a.stride(0),
+                             gate.stride(0), out.stride(0), float(lam), float(eps), float(post), _dta(a), _stream()),
+          "spd_heads_gate")
+    return out
 
 
 # ------------------------------------------------------------------------------------------------

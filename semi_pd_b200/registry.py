@@ -13,6 +13,7 @@ _MODELS: Dict[str, Tuple[str, str]] = {
     "rimidra": ("rimidra", "RimidraForCausalLM"),
     "nupovik": ("nupovik", "NupovikForCausalLM"),
     "matepel": ("matepel", "MatepelForCausalLM"),
+    "sugelix": ("sugelix", "SugelixForCausalLM"),
 }
 
 

@@ -45,13 +45,13 @@ class _W:
         self.weight: torch.Tensor = None
 
 
-def _rotary_table(rot_dims: int, base: float, max_positions: int, device) -> Optional[torch.Tensor]:
-    """fp32 [positions, rot_dims] = cos || sin of p · base^(-2 i / rot_dims), computed in float64 so
+def _rotary_table(rot_dims: int, base: float, max_positions: int, device, factor: float = 1.0) -> Optional[torch.Tensor]:
+    """fp32 [positions, rot_dims] = cos || sin of p · base^(-2 i / rot_dims) / factor, computed in float64 so
     the table holds the correctly rounded values even at large positions."""
     if rot_dims <= 0:
         return None
     i = torch.arange(rot_dims // 2, dtype=torch.float64)
-    freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / rot_dims)
+    freq = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / rot_dims) / float(factor)
     ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * freq[None, :]
     return torch.cat([ang.cos(), ang.sin()], dim=-1).to(torch.float32).to(device).contiguous()
 
@@ -59,10 +59,11 @@ def _rotary_table(rot_dims: int, base: float, max_positions: int, device) -> Opt
 _ROTARY_TABLES: Dict[tuple, torch.Tensor] = {}
 
 
-def _get_rotary_table(rot_dims, base, max_positions, device):
-    key = (int(rot_dims), float(base), int(max_positions), str(device))
+def _get_rotary_table(rot_dims, base, max_positions, device, factor: float = 1.0):
+    """Tables are shared by the layers (and layer runs) with the same rotation."""
+    key = (int(rot_dims), float(base), int(max_positions), str(device), float(factor))
     if key not in _ROTARY_TABLES:
-        _ROTARY_TABLES[key] = _rotary_table(rot_dims, base, max_positions, device)
+        _ROTARY_TABLES[key] = _rotary_table(rot_dims, base, max_positions, device, factor)
     return _ROTARY_TABLES[key]
 
 
