@@ -75,7 +75,7 @@ def parse_args():
     ap.add_argument("--no-roofline", action="store_true")
     ap.add_argument("--tp-steps", type=int, default=3)
     ap.add_argument("--clocks-csv", type=str, default="", help="write the nvidia-smi samples of the run here")
-    ap.add_argument("--family", type=str, default="", choices=["", "rimidra", "nupovik", "matepel"],
+    ap.add_argument("--family", type=str, default="", choices=["", "rimidra", "nupovik", "matepel", "sugelix"],
                     help="instead of the default workload: prefill / decode throughput and per-kernel rooflines of "
                          "that model family beside Llama (and, for nupovik and matepel, Rimidra) at equal size "
                          "(scripts/bench_rimidra.py, scripts/bench_nupovik.py, scripts/bench_matepel.py)")
